@@ -1,0 +1,797 @@
+// C ABI of the B200 batch SM120 SASS codec: context, kernels and launchers.
+//
+// Kernels are one thread per instruction word over a grid-stride loop.  A warp reads 32
+// consecutive 16-byte words (512 contiguous bytes) and writes 32 consecutive entries of
+// every output plane, so all global traffic is coalesced; the flat ISA table (about 300 KB)
+// stays in L1/L2 through the read-only path while the stream itself is loaded and stored
+// with streaming hints.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/cubit_b200.h"
+#include "codec_core.cuh"
+#include "elf_text.hpp"
+#include "flat_table.hpp"
+#include "isa_table.hpp"
+
+using namespace cubit;
+
+// ---- kernels -----------------------------------------------------------------------------
+
+namespace {
+
+constexpr int kBlock = 256;
+enum { CNT_DECODED = 0, CNT_REJECTED, CNT_TIE, CNT_EXACT, CNT_MISMATCH, CNT_WORDS };
+
+// Adds per-thread 0/1 tallies into the launch's counters: warp reduce, then one shared
+// atomic per warp, then one global atomic per block.
+template <int N>
+__device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int (&which)[N],
+                                            unsigned long long* counters) {
+    __shared__ uint32_t s_acc[CNT_WORDS];
+    if (threadIdx.x < CNT_WORDS) s_acc[threadIdx.x] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+        const uint32_t w = __reduce_add_sync(0xFFFFFFFFu, mine[k]);
+        if ((threadIdx.x & 31) == 0 && w) atomicAdd(&s_acc[which[k]], w);
+    }
+    __syncthreads();
+    if (threadIdx.x < CNT_WORDS && s_acc[threadIdx.x])
+        atomicAdd(&counters[threadIdx.x], (unsigned long long)s_acc[threadIdx.x]);
+}
+
+__global__ void __launch_bounds__(kBlock)
+decode_kernel(FlatView t, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
+              uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
+              unsigned long long* counters) {
+    uint32_t tally[3] = {0, 0, 0};
+    const uint64_t step = (uint64_t)gridDim.x * kBlock;
+    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+        const uint4 w = __ldcs(words + i);
+        uint32_t f, c, s[8];
+        decode_word(t, w.x, w.y, w.z, w.w, &f, s, &c);
+        __stcs(form + i, (uint16_t)f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) __stcs(slots + (uint64_t)k * slot_stride + i, s[k]);
+        __stcs(ctrl + i, c);
+        const bool ok = (c >> 30) == ST_OK;
+        tally[0] += ok; tally[1] += !ok; tally[2] += (c >> 28) & 1u;
+    }
+    if (counters) {
+        const int which[3] = {CNT_DECODED, CNT_REJECTED, CNT_TIE};
+        block_tally(tally, which, counters);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock)
+encode_kernel(FlatView t, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
+              uint64_t slot_stride, const uint32_t* __restrict__ ctrl, uint64_t n, uint4* __restrict__ words) {
+    const uint64_t step = (uint64_t)gridDim.x * kBlock;
+    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+        uint32_t s[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s[k] = __ldcs(slots + (uint64_t)k * slot_stride + i);
+        uint4 w;
+        encode_record(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
+        __stcs(words + i, w);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock)
+roundtrip_kernel(FlatView t, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
+                 unsigned long long* counters) {
+    uint32_t tally[3] = {0, 0, 0};
+    const uint64_t step = (uint64_t)gridDim.x * kBlock;
+    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+        const uint4 w = __ldcs(words + i);
+        const uint32_t st = roundtrip_word(t, w.x, w.y, w.z, w.w);
+        __stcs(status + i, (uint8_t)st);
+        tally[0] += st == RT_EXACT; tally[1] += st == RT_MISMATCH; tally[2] += st == RT_REJECTED;
+    }
+    if (counters) {
+        const int which[3] = {CNT_EXACT, CNT_MISMATCH, CNT_REJECTED};
+        block_tally(tally, which, counters);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock)
+synth_kernel(FlatView t, SynthView g, uint64_t first, uint64_t n, uint4* __restrict__ words,
+             uint16_t* __restrict__ form, uint32_t* __restrict__ slots, uint64_t slot_stride,
+             uint32_t* __restrict__ ctrl) {
+    const uint64_t step = (uint64_t)gridDim.x * kBlock;
+    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+        uint32_t f = FORM_NONE, c = 0, s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, w[4];
+        if (synth_record(t, g, first + i, &f, s, &c, w)) encode_record(t, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+        else c = ctrl_from_raw(w[0], w[3]);
+        if (words) words[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        if (form) form[i] = (uint16_t)f;
+        if (ctrl) ctrl[i] = c;
+        if (slots)
+            for (int k = 0; k < 8; ++k) slots[(uint64_t)k * slot_stride + i] = s[k];
+    }
+}
+
+// ---- context -----------------------------------------------------------------------------
+
+thread_local std::string g_create_error;
+
+struct DeviceState {
+    int device = -1;
+    int sm_count = 0;
+    FlatView view{};
+    std::vector<void*> table_allocs;
+    unsigned long long* counters = nullptr;   // kCounterSlots x CNT_WORDS
+    std::vector<int> free_counter_slots;
+    std::mutex mu;
+    // Grow-only staging for the host-memory paths.
+    void* stage = nullptr;
+    uint64_t stage_bytes = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex stage_mu;
+    // Stream generator tables, one per (mix, seed).
+    std::map<std::pair<uint32_t, uint64_t>, SynthView> synth;
+};
+constexpr int kCounterSlots = 64;
+
+}  // namespace
+
+struct cubit_ctx {
+    IsaTable table;
+    FlatTable flat;
+    std::vector<std::unique_ptr<DeviceState>> devs;
+    std::map<std::pair<std::string, std::string>, uint32_t> by_name;
+    std::vector<std::vector<cubit_field_info>> field_infos;
+    std::mutex err_mu;
+    std::map<std::thread::id, std::string> errors;
+    std::mutex synth_mu;
+};
+
+struct cubit_elf {
+    const uint8_t* bytes;
+    uint64_t len;
+    std::vector<TextSection> text;
+};
+
+namespace {
+
+int fail(const cubit_ctx* ctx, int code, const std::string& msg) {
+    if (ctx) {
+        cubit_ctx* c = const_cast<cubit_ctx*>(ctx);
+        std::lock_guard<std::mutex> g(c->err_mu);
+        c->errors[std::this_thread::get_id()] = msg;
+    } else {
+        g_create_error = msg;
+    }
+    return code;
+}
+
+#define CU_TRY(ctx, call)                                                                             \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(ctx, CUBIT_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));     \
+    } while (0)
+
+std::string bundled_table_path() {
+    Dl_info info;
+    if (dladdr((void*)&bundled_table_path, &info) && info.dli_fname) {
+        std::string p(info.dli_fname);
+        size_t slash = p.rfind('/');
+        std::string dir = slash == std::string::npos ? "." : p.substr(0, slash);
+        return dir + "/../tables/sm120.json";
+    }
+    return "tables/sm120.json";
+}
+
+template <typename T>
+int upload(cubit_ctx* ctx, DeviceState* d, const std::vector<T>& host, const T** out) {
+    void* p = nullptr;
+    const size_t bytes = std::max<size_t>(host.size() * sizeof(T), 16);
+    CU_TRY(ctx, cudaMalloc(&p, bytes));
+    d->table_allocs.push_back(p);
+    if (!host.empty()) CU_TRY(ctx, cudaMemcpy(p, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice));
+    *out = (const T*)p;
+    return CUBIT_OK;
+}
+
+int grid_for(const DeviceState* d, uint64_t n) {
+    const uint64_t blocks = (n + kBlock - 1) / kBlock;
+    const uint64_t cap = (uint64_t)d->sm_count * 8;   // whole waves of resident blocks
+    return (int)std::max<uint64_t>(1, std::min(blocks, cap));
+}
+
+DeviceState* device_of_pointer(cubit_ctx* ctx, const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged) return nullptr;
+    for (auto& d : ctx->devs)
+        if (d->device == a.device) return d.get();
+    return nullptr;
+}
+
+int take_counter_slot(DeviceState* d) {
+    std::lock_guard<std::mutex> g(d->mu);
+    if (d->free_counter_slots.empty()) return -1;
+    int s = d->free_counter_slots.back();
+    d->free_counter_slots.pop_back();
+    return s;
+}
+void give_counter_slot(DeviceState* d, int s) {
+    std::lock_guard<std::mutex> g(d->mu);
+    d->free_counter_slots.push_back(s);
+}
+
+void add_counts(cubit_counts* out, const unsigned long long* c) {
+    out->n_decoded += c[CNT_DECODED]; out->n_rejected += c[CNT_REJECTED]; out->n_tie += c[CNT_TIE];
+    out->n_exact += c[CNT_EXACT]; out->n_mismatch += c[CNT_MISMATCH];
+}
+
+// Runs `launch(counters)` on `stream` of device d; when counts are wanted, zeroes a counter
+// slot first and reads it back (which waits for the stream).
+template <typename Launch>
+int run_counted(cubit_ctx* ctx, DeviceState* d, cudaStream_t stream, cubit_counts* counts, Launch launch) {
+    if (!counts) {
+        launch((unsigned long long*)nullptr);
+        CU_TRY(ctx, cudaGetLastError());
+        return CUBIT_OK;
+    }
+    const int slot = take_counter_slot(d);
+    if (slot < 0) return fail(ctx, CUBIT_ERR_NOMEM, "too many counted calls in flight on one device");
+    unsigned long long* dc = d->counters + (size_t)slot * CNT_WORDS;
+    unsigned long long host[CNT_WORDS];
+    cudaError_t e = cudaMemsetAsync(dc, 0, sizeof host, stream);
+    if (e == cudaSuccess) { launch(dc); e = cudaGetLastError(); }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host, dc, sizeof host, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    give_counter_slot(d, slot);
+    if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string("counted launch: ") + cudaGetErrorString(e));
+    add_counts(counts, host);
+    return CUBIT_OK;
+}
+
+int ensure_stage(cubit_ctx* ctx, DeviceState* d, uint64_t bytes) {
+    if (d->stage_bytes >= bytes) return CUBIT_OK;
+    if (d->stage) { CU_TRY(ctx, cudaFree(d->stage)); d->stage = nullptr; d->stage_bytes = 0; }
+    CU_TRY(ctx, cudaMalloc(&d->stage, bytes));
+    d->stage_bytes = bytes;
+    return CUBIT_OK;
+}
+
+// Contiguous range of device k out of g for n items.
+void shard_range(uint64_t n, size_t g, size_t k, uint64_t* begin, uint64_t* end) {
+    *begin = n / g * k + std::min<uint64_t>(k, n % g);
+    *end = *begin + n / g + (k < n % g ? 1 : 0);
+}
+
+constexpr uint64_t kChunkWords = 1ull << 22;   // host paths stream the batch in 4 Mi-word chunks
+
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// Host-memory decode of words [begin, end) on one device, chunked through its staging area.
+int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t n_total, uint64_t begin,
+                      uint64_t end, uint16_t* form, uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
+    std::lock_guard<std::mutex> g(d->stage_mu);
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
+    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
+    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
+    int rc = ensure_stage(ctx, d, total);
+    if (rc) return rc;
+    uint8_t* st = (uint8_t*)d->stage;
+    for (uint64_t at = begin; at < end; at += chunk) {
+        const uint64_t m = std::min(chunk, end - at);
+        CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
+        rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
+            decode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, (uint16_t*)(st + o_form),
+                                                                     (uint32_t*)(st + o_slots), chunk,
+                                                                     (uint32_t*)(st + o_ctrl), dc);
+        });
+        if (rc) return rc;
+        CU_TRY(ctx, cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
+        for (int k = 0; k < 8; ++k)
+            CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)k * n_total + at, st + o_slots + (uint64_t)k * chunk * 4, m * 4,
+                                        cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    }
+    return CUBIT_OK;
+}
+
+int encode_host_range(cubit_ctx* ctx, DeviceState* d, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl,
+                      uint64_t n_total, uint64_t begin, uint64_t end, uint8_t* words) {
+    std::lock_guard<std::mutex> g(d->stage_mu);
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
+    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
+    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
+    int rc = ensure_stage(ctx, d, total);
+    if (rc) return rc;
+    uint8_t* st = (uint8_t*)d->stage;
+    for (uint64_t at = begin; at < end; at += chunk) {
+        const uint64_t m = std::min(chunk, end - at);
+        CU_TRY(ctx, cudaMemcpyAsync(st + o_form, form + at, m * 2, cudaMemcpyHostToDevice, d->stream));
+        for (int k = 0; k < 8; ++k)
+            CU_TRY(ctx, cudaMemcpyAsync(st + o_slots + (uint64_t)k * chunk * 4, slots + (uint64_t)k * n_total + at, m * 4,
+                                        cudaMemcpyHostToDevice, d->stream));
+        CU_TRY(ctx, cudaMemcpyAsync(st + o_ctrl, ctrl + at, m * 4, cudaMemcpyHostToDevice, d->stream));
+        encode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint16_t*)(st + o_form),
+                                                                 (const uint32_t*)(st + o_slots), chunk,
+                                                                 (const uint32_t*)(st + o_ctrl), m, (uint4*)st);
+        CU_TRY(ctx, cudaGetLastError());
+        CU_TRY(ctx, cudaMemcpyAsync(words + at * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    }
+    return CUBIT_OK;
+}
+
+int roundtrip_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t begin, uint64_t end,
+                         uint8_t* status, cubit_counts* counts) {
+    std::lock_guard<std::mutex> g(d->stage_mu);
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
+    const uint64_t o_status = align_up(chunk * 16, 256), total = o_status + chunk;
+    int rc = ensure_stage(ctx, d, total);
+    if (rc) return rc;
+    uint8_t* st = (uint8_t*)d->stage;
+    for (uint64_t at = begin; at < end; at += chunk) {
+        const uint64_t m = std::min(chunk, end - at);
+        CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
+        rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
+            roundtrip_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, st + o_status, dc);
+        });
+        if (rc) return rc;
+        CU_TRY(ctx, cudaMemcpyAsync(status + at, st + o_status, m, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    }
+    return CUBIT_OK;
+}
+
+// Runs fn(device index) for every device of the context on its own host thread and merges
+// the per-device counts and status codes.
+template <typename Fn>
+int for_each_device(cubit_ctx* ctx, cubit_counts* counts, Fn fn) {
+    const size_t g = ctx->devs.size();
+    std::vector<int> rcs(g, CUBIT_OK);
+    std::vector<cubit_counts> partial(g);
+    std::vector<std::string> messages(g);
+    memset(partial.data(), 0, g * sizeof(cubit_counts));
+    auto body = [&](size_t k) {
+        rcs[k] = fn(k, counts ? &partial[k] : nullptr);
+        if (rcs[k]) messages[k] = cubit_last_error(ctx);
+    };
+    if (g == 1) {
+        body(0);
+    } else {
+        std::vector<std::thread> th;
+        for (size_t k = 0; k < g; ++k) th.emplace_back(body, k);
+        for (auto& t : th) t.join();
+    }
+    for (size_t k = 0; k < g; ++k)
+        if (rcs[k]) return fail(ctx, rcs[k], messages[k]);
+    if (counts)
+        for (size_t k = 0; k < g; ++k) {
+            counts->n_decoded += partial[k].n_decoded; counts->n_rejected += partial[k].n_rejected;
+            counts->n_tie += partial[k].n_tie; counts->n_exact += partial[k].n_exact;
+            counts->n_mismatch += partial[k].n_mismatch;
+        }
+    return CUBIT_OK;
+}
+
+int get_synth_view(cubit_ctx* ctx, DeviceState* d, uint32_t mix, uint64_t seed, uint32_t noise_ppm, SynthView* out) {
+    std::lock_guard<std::mutex> g(ctx->synth_mu);
+    const uint64_t table_seed = mix == MIX_ZIPF ? seed : 0;   // only the Zipf permutation depends on the seed
+    auto key = std::make_pair(mix, table_seed);
+    auto it = d->synth.find(key);
+    if (it == d->synth.end()) {
+        SynthTables st;
+        try {
+            st = build_synth_tables(ctx->table, mix, seed);
+        } catch (const std::exception& e) {
+            return fail(ctx, CUBIT_ERR_INVALID, e.what());
+        }
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        SynthView v{};
+        int rc = upload(ctx, d, st.cdf, &v.cdf);
+        if (!rc) rc = upload(ctx, d, st.rank_first, &v.rank_first);
+        if (!rc) rc = upload(ctx, d, st.rank_count, &v.rank_count);
+        if (rc) return rc;
+        v.n_ranks = (uint32_t)st.cdf.size();
+        it = d->synth.emplace(key, v).first;
+    }
+    *out = it->second;
+    out->seed = seed;
+    out->noise_ppm = noise_ppm;
+    return CUBIT_OK;
+}
+
+}  // namespace
+
+// ---- exported: context ------------------------------------------------------------------------
+
+extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int n_devices, cubit_ctx** out) {
+    if (!out || n_devices < 0 || (n_devices > 0 && !devices)) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
+    *out = nullptr;
+    std::unique_ptr<cubit_ctx> ctx(new cubit_ctx);
+    std::string path;
+    const char* env = getenv("CUBIT_TABLE");
+    if (env && *env) path = env;
+    else if (table_path && *table_path) path = table_path;
+    else path = bundled_table_path();
+    try {
+        ctx->table = IsaTable::from_file(path);
+        ctx->flat = FlatTable::compile(ctx->table);
+    } catch (const std::exception& e) {
+        return fail(nullptr, CUBIT_ERR_TABLE, std::string("table ") + path + ": " + e.what());
+    }
+    const FlatTable& ft = ctx->flat;
+    ctx->field_infos.resize(ft.meta.size());
+    for (size_t v = 0; v < ft.meta.size(); ++v) {
+        ctx->by_name[{ft.meta[v].key, ft.meta[v].mod_group}] = (uint32_t)v;
+        for (const FieldMeta& f : ft.meta[v].fields)
+            ctx->field_infos[v].push_back(
+                cubit_field_info{f.shift, f.bits, f.token_idx, f.dst_pos, f.name.c_str(), f.extraction.c_str()});
+    }
+    for (int k = 0; k < n_devices; ++k) {
+        std::unique_ptr<DeviceState> d(new DeviceState);
+        d->device = devices[k];
+        cubit_ctx* c = nullptr;   // failures during creation report through the thread-local message
+        CU_TRY(c, cudaSetDevice(d->device));
+        CU_TRY(c, cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, d->device));
+        int rc = upload(c, d.get(), ft.bucket_dir, &d->view.bucket_dir);
+        if (!rc) rc = upload(c, d.get(), ft.cand, &d->view.cand);
+        if (!rc) rc = upload(c, d.get(), ft.var, &d->view.var);
+        if (!rc) rc = upload(c, d.get(), ft.pieces, &d->view.pieces);
+        if (!rc) rc = upload(c, d.get(), ft.gfields, &d->view.gfields);
+        if (rc) return rc;
+        d->view.n_variants = (uint32_t)ft.meta.size();
+        CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
+        for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
+        CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+        ctx->devs.push_back(std::move(d));
+    }
+    *out = ctx.release();
+    return CUBIT_OK;
+}
+
+extern "C" void cubit_ctx_destroy(cubit_ctx* ctx) {
+    if (!ctx) return;
+    for (auto& d : ctx->devs) {
+        cudaSetDevice(d->device);
+        cudaDeviceSynchronize();
+        for (void* p : d->table_allocs) cudaFree(p);
+        if (d->counters) cudaFree(d->counters);
+        if (d->stage) cudaFree(d->stage);
+        if (d->stream) cudaStreamDestroy(d->stream);
+    }
+    delete ctx;
+}
+
+extern "C" const char* cubit_last_error(const cubit_ctx* ctx) {
+    if (!ctx) return g_create_error.c_str();
+    cubit_ctx* c = const_cast<cubit_ctx*>(ctx);
+    std::lock_guard<std::mutex> g(c->err_mu);
+    return c->errors[std::this_thread::get_id()].c_str();
+}
+
+extern "C" int cubit_table_info(const cubit_ctx* ctx, uint32_t* n_keys, uint32_t* n_groups) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (n_keys) *n_keys = (uint32_t)ctx->table.num_keys();
+    if (n_groups) *n_groups = (uint32_t)ctx->table.num_groups();
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_variant_lookup(const cubit_ctx* ctx, uint32_t variant, cubit_variant_info* out) {
+    if (!ctx || !out) return CUBIT_ERR_INVALID;
+    if (variant >= ctx->flat.meta.size()) return fail(ctx, CUBIT_ERR_NOT_FOUND, "variant id out of range");
+    const VariantMeta& m = ctx->flat.meta[variant];
+    out->key = m.key.c_str(); out->mod_group = m.mod_group.c_str(); out->opcode = m.opcode.c_str();
+    out->key_id = m.key_id; out->layout_kind = m.layout_kind; out->synth_mask = m.synth_mask;
+    out->ra_tok = m.ra_tok; out->rb_tok = m.rb_tok;
+    out->n_fields = (uint32_t)m.fields.size();
+    out->fields = ctx->field_infos[variant].data();
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_variant_find(const cubit_ctx* ctx, const char* key, const char* mod_group, uint32_t* variant) {
+    if (!ctx || !key || !mod_group || !variant) return CUBIT_ERR_INVALID;
+    auto it = ctx->by_name.find({key, mod_group});
+    if (it == ctx->by_name.end()) return fail(ctx, CUBIT_ERR_NOT_FOUND, std::string("no table entry ") + key + "::" + mod_group);
+    *variant = it->second;
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_key_name(const cubit_ctx* ctx, uint32_t key_id, const char** name, uint32_t* first_variant,
+                              uint32_t* n_variants) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (key_id >= ctx->table.keys.size()) return fail(ctx, CUBIT_ERR_NOT_FOUND, "key id out of range");
+    const IsaKey& k = ctx->table.keys[key_id];
+    if (name) *name = k.name.c_str();
+    if (first_variant) *first_variant = k.first_variant;
+    if (n_variants) *n_variants = k.n_variants;
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_host_alloc(cubit_ctx* ctx, uint64_t bytes, void** out) {
+    if (!ctx || !out) return CUBIT_ERR_INVALID;
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "context has no CUDA device");
+    CU_TRY(ctx, cudaSetDevice(ctx->devs[0]->device));
+    CU_TRY(ctx, cudaHostAlloc(out, std::max<uint64_t>(bytes, 1), cudaHostAllocPortable));
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_host_free(cubit_ctx* ctx, void* p) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (p) CU_TRY(ctx, cudaFreeHost(p));
+    return CUBIT_OK;
+}
+
+// ---- exported: batch codec ----------------------------------------------------------------------
+
+extern "C" int cubit_decode_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint16_t* form, uint32_t* slots,
+                                  uint32_t* ctrl, cubit_counts* counts, int mem_kind, void* stream) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (counts) memset(counts, 0, sizeof *counts);
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "decode needs a CUDA device; this context has none");
+    if (n == 0) return CUBIT_OK;
+    if (!words || !form || !slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
+    if (mem_kind == CUBIT_MEM_DEVICE) {
+        DeviceState* d = device_of_pointer(ctx, words);
+        if (!d) return fail(ctx, CUBIT_ERR_INVALID, "words is not device memory of one of the context's devices");
+        if ((uintptr_t)words % 16) return fail(ctx, CUBIT_ERR_INVALID, "device words must be 16-byte aligned");
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        cudaStream_t s = (cudaStream_t)stream;
+        return run_counted(ctx, d, s, counts, [&](unsigned long long* dc) {
+            decode_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, (const uint4*)words, n, form, slots, n, ctrl, dc);
+        });
+    }
+    if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
+    const size_t g = ctx->devs.size();
+    return for_each_device(ctx, counts, [&](size_t k, cubit_counts* part) {
+        uint64_t b, e;
+        shard_range(n, g, k, &b, &e);
+        if (b == e) return (int)CUBIT_OK;
+        return decode_host_range(ctx, ctx->devs[k].get(), (const uint8_t*)words, n, b, e, form, slots, ctrl, part);
+    });
+}
+
+extern "C" int cubit_encode_batch(cubit_ctx* ctx, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl,
+                                  uint64_t n, void* words, int mem_kind, void* stream) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "encode needs a CUDA device; this context has none");
+    if (n == 0) return CUBIT_OK;
+    if (!words || !form || !slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
+    if (mem_kind == CUBIT_MEM_DEVICE) {
+        DeviceState* d = device_of_pointer(ctx, words);
+        if (!d) return fail(ctx, CUBIT_ERR_INVALID, "words is not device memory of one of the context's devices");
+        if ((uintptr_t)words % 16) return fail(ctx, CUBIT_ERR_INVALID, "device words must be 16-byte aligned");
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        cudaStream_t s = (cudaStream_t)stream;
+        encode_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, form, slots, n, ctrl, n, (uint4*)words);
+        CU_TRY(ctx, cudaGetLastError());
+        return CUBIT_OK;
+    }
+    if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
+    const size_t g = ctx->devs.size();
+    return for_each_device(ctx, nullptr, [&](size_t k, cubit_counts*) {
+        uint64_t b, e;
+        shard_range(n, g, k, &b, &e);
+        if (b == e) return (int)CUBIT_OK;
+        return encode_host_range(ctx, ctx->devs[k].get(), form, slots, ctrl, n, b, e, (uint8_t*)words);
+    });
+}
+
+extern "C" int cubit_roundtrip_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint8_t* status,
+                                     cubit_counts* counts, int mem_kind, void* stream) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (counts) memset(counts, 0, sizeof *counts);
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "roundtrip needs a CUDA device; this context has none");
+    if (n == 0) return CUBIT_OK;
+    if (!words || !status) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
+    if (mem_kind == CUBIT_MEM_DEVICE) {
+        DeviceState* d = device_of_pointer(ctx, words);
+        if (!d) return fail(ctx, CUBIT_ERR_INVALID, "words is not device memory of one of the context's devices");
+        if ((uintptr_t)words % 16) return fail(ctx, CUBIT_ERR_INVALID, "device words must be 16-byte aligned");
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        cudaStream_t s = (cudaStream_t)stream;
+        return run_counted(ctx, d, s, counts, [&](unsigned long long* dc) {
+            roundtrip_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, (const uint4*)words, n, status, dc);
+        });
+    }
+    if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
+    const size_t g = ctx->devs.size();
+    return for_each_device(ctx, counts, [&](size_t k, cubit_counts* part) {
+        uint64_t b, e;
+        shard_range(n, g, k, &b, &e);
+        if (b == e) return (int)CUBIT_OK;
+        return roundtrip_host_range(ctx, ctx->devs[k].get(), (const uint8_t*)words, b, e, status, part);
+    });
+}
+
+extern "C" int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first,
+                                 uint64_t n, void* words, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int mem_kind,
+                                 void* stream) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "the stream generator needs a CUDA device");
+    if (n == 0) return CUBIT_OK;
+    if (noise_ppm > 1000000) return fail(ctx, CUBIT_ERR_INVALID, "noise_ppm above one million");
+    if (mem_kind == CUBIT_MEM_DEVICE) {
+        const void* probe = words ? words : (form ? (const void*)form : (slots ? (const void*)slots : (const void*)ctrl));
+        if (!probe) return fail(ctx, CUBIT_ERR_INVALID, "no output buffer");
+        DeviceState* d = device_of_pointer(ctx, probe);
+        if (!d) return fail(ctx, CUBIT_ERR_INVALID, "output is not device memory of one of the context's devices");
+        SynthView g;
+        int rc = get_synth_view(ctx, d, mix, seed, noise_ppm, &g);
+        if (rc) return rc;
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        cudaStream_t s = (cudaStream_t)stream;
+        synth_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, g, first, n, (uint4*)words, form, slots, n, ctrl);
+        CU_TRY(ctx, cudaGetLastError());
+        return CUBIT_OK;
+    }
+    if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
+    // Host output: generate on the first device in chunks and copy back.
+    DeviceState* d = ctx->devs[0].get();
+    SynthView g;
+    int rc = get_synth_view(ctx, d, mix, seed, noise_ppm, &g);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(d->stage_mu);
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    const uint64_t chunk = std::min<uint64_t>(kChunkWords, n);
+    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
+    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
+    rc = ensure_stage(ctx, d, total);
+    if (rc) return rc;
+    uint8_t* st = (uint8_t*)d->stage;
+    for (uint64_t at = 0; at < n; at += chunk) {
+        const uint64_t m = std::min(chunk, n - at);
+        synth_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, g, first + at, m, (uint4*)st, (uint16_t*)(st + o_form),
+                                                                (uint32_t*)(st + o_slots), chunk, (uint32_t*)(st + o_ctrl));
+        CU_TRY(ctx, cudaGetLastError());
+        if (words) CU_TRY(ctx, cudaMemcpyAsync((uint8_t*)words + at * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
+        if (form) CU_TRY(ctx, cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
+        if (slots)
+            for (int k = 0; k < 8; ++k)
+                CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)k * n + at, st + o_slots + (uint64_t)k * chunk * 4, m * 4,
+                                            cudaMemcpyDeviceToHost, d->stream));
+        if (ctrl) CU_TRY(ctx, cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    }
+    return CUBIT_OK;
+}
+
+// ---- exported: cubin ----------------------------------------------------------------------------
+
+extern "C" int cubit_elf_parse(const void* bytes, uint64_t len, cubit_elf** out) {
+    if (!bytes || !out) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
+    *out = nullptr;
+    std::unique_ptr<cubit_elf> e(new cubit_elf);
+    e->bytes = (const uint8_t*)bytes;
+    e->len = len;
+    try {
+        e->text = elf_text_sections(e->bytes, len);
+    } catch (const std::exception& ex) {
+        return fail(nullptr, CUBIT_ERR_ELF, ex.what());
+    }
+    *out = e.release();
+    return CUBIT_OK;
+}
+
+extern "C" void cubit_elf_free(cubit_elf* elf) { delete elf; }
+
+extern "C" uint32_t cubit_elf_num_text(const cubit_elf* elf) { return elf ? (uint32_t)elf->text.size() : 0; }
+
+extern "C" int cubit_elf_text(const cubit_elf* elf, uint32_t index, const char** name, uint64_t* offset, uint64_t* size) {
+    if (!elf || index >= elf->text.size()) return fail(nullptr, CUBIT_ERR_INVALID, "text section index out of range");
+    if (name) *name = elf->text[index].name.c_str();
+    if (offset) *offset = elf->text[index].offset;
+    if (size) *size = elf->text[index].size;
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_elf_find(const cubit_elf* elf, const char* kernel_name, uint32_t* index) {
+    if (!elf || !kernel_name || !index) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
+    for (size_t i = 0; i < elf->text.size(); ++i)
+        if (elf->text[i].name.find(kernel_name) != std::string::npos) {
+            *index = (uint32_t)i;
+            return CUBIT_OK;
+        }
+    std::string names;
+    for (const TextSection& t : elf->text) names += (names.empty() ? "\"" : ", \"") + t.name + "\"";
+    return fail(nullptr, CUBIT_ERR_NOT_FOUND, std::string("kernel '") + kernel_name + "' not found. Available: [" + names + "]");
+}
+
+extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indices, uint32_t n_sections,
+                                uint64_t* word_start, uint64_t capacity, uint16_t* form, uint32_t* slots,
+                                uint32_t* ctrl, void* raw_words, cubit_counts* counts) {
+    if (!ctx || !elf || !word_start) return fail(ctx, CUBIT_ERR_INVALID, "bad argument");
+    if (counts) memset(counts, 0, sizeof *counts);
+    if (!indices) n_sections = (uint32_t)elf->text.size();
+    // Per-kernel offset table: record index of each section's first word.
+    struct Range { uint64_t file_off, words, rec; };
+    std::vector<Range> ranges;
+    uint64_t total = 0;
+    for (uint32_t k = 0; k < n_sections; ++k) {
+        const uint32_t si = indices ? indices[k] : k;
+        if (si >= elf->text.size()) return fail(ctx, CUBIT_ERR_INVALID, "text section index out of range");
+        const TextSection& t = elf->text[si];
+        if (t.offset > elf->len || t.size > elf->len - t.offset)
+            return fail(ctx, CUBIT_ERR_ELF, "text section " + t.name + " extends past end of file");
+        word_start[k] = total;
+        const uint64_t w = t.size / 16;
+        // Sections that follow each other in the file are fetched with one copy.
+        if (!ranges.empty() && ranges.back().file_off + ranges.back().words * 16 == t.offset && w)
+            ranges.back().words += w;
+        else if (w)
+            ranges.push_back(Range{t.offset, w, total});
+        total += w;
+    }
+    word_start[n_sections] = total;
+    if (!form) return CUBIT_OK;
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "decode needs a CUDA device; this context has none");
+    if (!slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
+    if (capacity < total) return fail(ctx, CUBIT_ERR_INVALID, "output capacity below the number of words");
+    if (total == 0) return CUBIT_OK;
+
+    // Shard records over devices by cumulative word count; each device gathers its part of
+    // the text ranges into one contiguous staging buffer and decodes it in a single launch.
+    const size_t g = ctx->devs.size();
+    return for_each_device(ctx, counts, [&](size_t k, cubit_counts* part) {
+        uint64_t b, e;
+        shard_range(total, g, k, &b, &e);
+        if (b == e) return (int)CUBIT_OK;
+        DeviceState* d = ctx->devs[k].get();
+        std::lock_guard<std::mutex> lock(d->stage_mu);
+        CU_TRY(ctx, cudaSetDevice(d->device));
+        const uint64_t m = e - b;
+        const uint64_t o_form = align_up(m * 16, 256), o_slots = o_form + align_up(m * 2, 256);
+        const uint64_t o_ctrl = o_slots + m * 32, bytes = o_ctrl + m * 4;
+        int rc = ensure_stage(ctx, d, bytes);
+        if (rc) return rc;
+        uint8_t* st = (uint8_t*)d->stage;
+        for (const Range& r : ranges) {
+            const uint64_t lo = std::max(b, r.rec), hi = std::min(e, r.rec + r.words);
+            if (lo >= hi) continue;
+            const uint8_t* src = elf->bytes + r.file_off + (lo - r.rec) * 16;
+            CU_TRY(ctx, cudaMemcpyAsync(st + (lo - b) * 16, src, (hi - lo) * 16, cudaMemcpyHostToDevice, d->stream));
+        }
+        rc = run_counted(ctx, d, d->stream, part, [&](unsigned long long* dc) {
+            decode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, (uint16_t*)(st + o_form),
+                                                                     (uint32_t*)(st + o_slots), m, (uint32_t*)(st + o_ctrl), dc);
+        });
+        if (rc) return rc;
+        CU_TRY(ctx, cudaMemcpyAsync(form + b, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
+        for (int s = 0; s < 8; ++s)
+            CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)s * capacity + b, st + o_slots + (uint64_t)s * m * 4, m * 4,
+                                        cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaMemcpyAsync(ctrl + b, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
+        if (raw_words) CU_TRY(ctx, cudaMemcpyAsync((uint8_t*)raw_words + b * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+        return (int)CUBIT_OK;
+    });
+}
+
+extern "C" int cubit_elf_build(const char* const* names, const void* const* code, const uint64_t* code_bytes,
+                               uint32_t n_kernels, void* out, uint64_t capacity, uint64_t* out_len) {
+    if (!out_len || (n_kernels && (!names || !code || !code_bytes))) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
+    std::vector<BuildKernel> ks;
+    for (uint32_t k = 0; k < n_kernels; ++k) ks.push_back(BuildKernel{names[k], (const uint8_t*)code[k], code_bytes[k]});
+    try {
+        *out_len = elf_build(ks, (uint8_t*)out, capacity);
+    } catch (const std::exception& e) {
+        return fail(nullptr, CUBIT_ERR_ELF, e.what());
+    }
+    return CUBIT_OK;
+}

@@ -1,0 +1,173 @@
+/*
+ * cubit_b200 — C ABI of the B200 batch SM120 SASS codec.
+ *
+ * The reference (kacper-daftcode/cubit, a Rust crate) exposes this path only through its
+ * Rust library API and a PyO3 module; it has no C ABI of its own.  Each entry point below
+ * names the reference interface it stands in for.  All functions return 0 on success or a
+ * negative cubit_status; none of them throws or aborts.  The caller owns every buffer.
+ * A context is immutable after creation and may be used from several host threads at once.
+ *
+ * Words are 16 bytes, little-endian: bytes 0..7 = lo64, bytes 8..15 = hi64
+ * (reference src/python.rs:127-129).
+ *
+ * A decoded record is structure-of-arrays:
+ *   form  u16[n]      variant id (index of (key, mod_group) in bytewise order), 0xFFFF = rejected
+ *   slots u32[8][n]   slot-major: slot s of record i is slots[s * n + i]
+ *   ctrl  u32[n]      [16:0] scheduling word (wait|rbar|wbar|yield|stall), [19:17] reuse bits,
+ *                     [23:20] guard nibble, [27:24] synthesized abs/neg presence (bits 63,62,72,73),
+ *                     [28] tie, [31:30] status (0 ok, 1 unknown opcode bits, 2 no variant matches)
+ * Where each table field of a variant lives inside the 8 slots is static per variant and
+ * reported by cubit_variant_lookup (cubit_field_info.dst_pos).
+ */
+#ifndef CUBIT_B200_H
+#define CUBIT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cubit_ctx cubit_ctx;
+typedef struct cubit_elf cubit_elf;
+
+typedef enum {
+    CUBIT_OK = 0,
+    CUBIT_ERR_INVALID = -1,    /* bad argument */
+    CUBIT_ERR_TABLE = -2,      /* ISA table missing, malformed or too large */
+    CUBIT_ERR_CUDA = -3,       /* a CUDA call failed; see cubit_last_error */
+    CUBIT_ERR_NO_DEVICE = -4,  /* compute entry point called on a context without a GPU */
+    CUBIT_ERR_ELF = -5,        /* not a little-endian ELF64, or truncated */
+    CUBIT_ERR_NOT_FOUND = -6,  /* kernel / variant name not found */
+    CUBIT_ERR_NOMEM = -7
+} cubit_status;
+
+enum { CUBIT_MEM_HOST = 0, CUBIT_MEM_DEVICE = 1 };
+enum { CUBIT_MIX_UNIFORM = 0, CUBIT_MIX_ZIPF = 1, CUBIT_MIX_FAMILY = 2 };
+enum { CUBIT_FORM_NONE = 0xFFFF };
+enum { CUBIT_RT_EXACT = 0, CUBIT_RT_MISMATCH = 1, CUBIT_RT_REJECTED = 2 };
+
+typedef struct {
+    uint64_t n_decoded;   /* decode / roundtrip: words that selected a variant */
+    uint64_t n_rejected;  /* words that match no variant */
+    uint64_t n_tie;       /* decoded words whose winner was separated only by canonical order */
+    uint64_t n_exact;     /* roundtrip: re-encoded word equals the input outside bits 121:105 */
+    uint64_t n_mismatch;  /* roundtrip: it does not */
+} cubit_counts;
+
+typedef struct {
+    uint32_t shift, bits;
+    int32_t token_idx;
+    uint32_t dst_pos;        /* bit position of the value in the 256-bit slot area (slot = pos/32) */
+    const char* name;        /* "Rd", "Ra", "Rb", "Rc", "guard" or "[hi:lo]" */
+    const char* extraction;  /* spelling reported by the reference decoder */
+} cubit_field_info;
+
+typedef struct {
+    const char* key;
+    const char* mod_group;
+    const char* opcode;
+    uint32_t key_id;
+    uint32_t layout_kind;    /* 0 = one slot per multi-bit field + shared flag slot, 1 = dense */
+    uint32_t synth_mask;     /* which of bits 63, 62, 72, 73 can carry a synthesized neg/abs */
+    int32_t ra_tok, rb_tok;  /* token index reported for synthesized Ra / Rb modifiers */
+    uint32_t n_fields;
+    const cubit_field_info* fields;
+} cubit_variant_info;
+
+/* ---- context ------------------------------------------------------------------------ */
+
+/* Replaces IsaTable::load_default + DecodeIndex::build (reference src/table.rs:239-249,
+ * src/decoder.rs:80-160; the process-global pair of src/python.rs:28-42).  Table source:
+ * $CUBIT_TABLE if set (strict), else `table_path`, else the copy bundled with the library.
+ * The table is compiled to flat arrays and uploaded to each listed CUDA device.
+ * n_devices == 0 gives a host-only context: metadata and ELF helpers work, compute entry
+ * points return CUBIT_ERR_NO_DEVICE.  On failure *out is NULL and cubit_last_error(NULL)
+ * describes why. */
+int cubit_ctx_create(const char* table_path, const int* devices, int n_devices, cubit_ctx** out);
+void cubit_ctx_destroy(cubit_ctx* ctx);
+
+/* Message of the last failure on this thread for `ctx` (NULL: for cubit_ctx_create / ELF helpers).
+ * Mirrors the reference's anyhow error strings (src/decoder.rs:173, :287). */
+const char* cubit_last_error(const cubit_ctx* ctx);
+
+/* Replaces table_info() (reference src/python.rs:171-177): (2001, 2872) for the bundled table. */
+int cubit_table_info(const cubit_ctx* ctx, uint32_t* n_keys, uint32_t* n_groups);
+
+/* Static description of one variant: what a host needs to rebuild the reference's DecodedInst
+ * (src/decoder.rs:32-47) from a record.  Pointers stay valid until cubit_ctx_destroy. */
+int cubit_variant_lookup(const cubit_ctx* ctx, uint32_t variant, cubit_variant_info* out);
+/* Replaces IsaTable::get (reference src/table.rs:406-408). */
+int cubit_variant_find(const cubit_ctx* ctx, const char* key, const char* mod_group, uint32_t* variant);
+int cubit_key_name(const cubit_ctx* ctx, uint32_t key_id, const char** name, uint32_t* first_variant,
+                   uint32_t* n_variants);
+
+/* Pinned host memory for the CUBIT_MEM_HOST paths (plain malloc'd memory also works, slower). */
+int cubit_host_alloc(cubit_ctx* ctx, uint64_t bytes, void** out);
+int cubit_host_free(cubit_ctx* ctx, void* p);
+
+/* ---- batch codec ---------------------------------------------------------------------- */
+
+/* Replaces a loop of DecodeIndex::decode (reference src/decoder.rs:163-382) over n words.
+ * mem_kind HOST: buffers are host memory; the words are split into contiguous ranges over
+ * the context's devices, copied in, decoded and copied back.  DEVICE: buffers live on one of
+ * the context's devices and the kernel is queued on `stream` (a cudaStream_t, NULL = default);
+ * the call returns without waiting unless `counts` is given.  `counts` may be NULL. */
+int cubit_decode_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint16_t* form, uint32_t* slots,
+                       uint32_t* ctrl, cubit_counts* counts, int mem_kind, void* stream);
+
+/* Record -> word: the table-driven core of encode_instruction (reference src/encoder.rs:293-300,
+ * :341-384, :530-532, :560-608, :1155-1179) applied to records instead of parsed text.
+ * form >= number of variants gives a zero word. */
+int cubit_encode_batch(cubit_ctx* ctx, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl,
+                       uint64_t n, void* words, int mem_kind, void* stream);
+
+/* Fused decode -> encode -> compare outside the scheduling field, the per-word faithfulness
+ * check of the reference (src/main.rs:270, :578-581, :717-737) at record level.
+ * status[i] is CUBIT_RT_EXACT / MISMATCH / REJECTED. */
+int cubit_roundtrip_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint8_t* status,
+                          cubit_counts* counts, int mem_kind, void* stream);
+
+/* Seeded synthetic instruction stream, words [first, first + n) of the stream (mix, seed,
+ * noise_ppm); any range can be produced on its own, so shards of one stream agree bit for bit.
+ * words / form / slots / ctrl may each be NULL.  Records are the generator's own (the input of
+ * an encode benchmark); noise words have form 0xFFFF.  No counterpart in the reference, whose
+ * corpus is private. */
+int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first,
+                      uint64_t n, void* words, uint16_t* form, uint32_t* slots, uint32_t* ctrl,
+                      int mem_kind, void* stream);
+
+/* ---- cubin (ELF) ------------------------------------------------------------------------ */
+
+/* Replaces CubinFile::from_bytes (reference src/elf.rs:29-58): lists PROGBITS sections named
+ * ".text" or ".text.*" with size > 0, in section-header order.  `bytes` must outlive the handle. */
+int cubit_elf_parse(const void* bytes, uint64_t len, cubit_elf** out);
+void cubit_elf_free(cubit_elf* elf);
+uint32_t cubit_elf_num_text(const cubit_elf* elf);
+int cubit_elf_text(const cubit_elf* elf, uint32_t index, const char** name, uint64_t* offset, uint64_t* size);
+/* First text section whose name contains `kernel_name` (reference src/python.rs:113-114). */
+int cubit_elf_find(const cubit_elf* elf, const char* kernel_name, uint32_t* index);
+
+/* Replaces the per-word loop of decode_kernel (reference src/python.rs:124-167) for many
+ * kernels at once: every 16-byte word of the chosen text sections (indices == NULL: all) is
+ * decoded in one launch per device.  word_start[k] (n_sections + 1 entries, output) is the
+ * record index of the first word of section k; a trailing partial word is ignored.
+ * Output buffers are host memory with room for `capacity` records; `raw_words` (optional)
+ * receives the 16-byte words in record order.  Call with form == NULL to get only word_start. */
+int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indices, uint32_t n_sections,
+                     uint64_t* word_start, uint64_t capacity, uint16_t* form, uint32_t* slots,
+                     uint32_t* ctrl, void* raw_words, cubit_counts* counts);
+
+/* Synthetic multi-kernel cubin with the section layout of the reference's Mercury-free
+ * builder (src/elf_builder.rs:535-847): 9 + 4N sections, one ".text.<name>" per kernel,
+ * 128-byte aligned and padded with NOPs plus one trailing self-branch.  Note and info
+ * sections carry placeholder contents; the result is an input for cubit_elf_parse, not a
+ * loadable module.  Call with out == NULL to get the required size in *out_len. */
+int cubit_elf_build(const char* const* names, const void* const* code, const uint64_t* code_bytes,
+                    uint32_t n_kernels, void* out, uint64_t capacity, uint64_t* out_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUBIT_B200_H */

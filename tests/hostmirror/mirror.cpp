@@ -1,0 +1,106 @@
+// TEST-ONLY harness: runs the per-word codec core (cubit_b200/csrc/codec_core.cuh, the text the
+// CUDA kernels are compiled from) as plain C++ over the host copy of the flat table, so the
+// flat-table logic can be compared with the oracle on a machine without a GPU.  It is not
+// linked into, loaded by, or reachable from the product library.
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../cubit_b200/csrc/codec_core.cuh"
+#include "../../cubit_b200/csrc/flat_table.hpp"
+#include "../../cubit_b200/csrc/isa_table.hpp"
+
+using namespace cubit;
+
+struct Mirror {
+    IsaTable table;
+    FlatTable flat;
+    FlatView view;
+};
+
+static thread_local std::string g_err;
+
+template <typename Fn>
+static void pfor(uint64_t n, int threads, Fn fn) {
+    if (threads <= 1 || n < 4096) { fn(0, n); return; }
+    std::vector<std::thread> th;
+    for (int k = 0; k < threads; ++k)
+        th.emplace_back([=] { fn(n * (uint64_t)k / threads, n * (uint64_t)(k + 1) / threads); });
+    for (auto& t : th) t.join();
+}
+
+extern "C" {
+const char* mir_last_error() { return g_err.c_str(); }
+void* mir_load(const char* path) {
+    try {
+        Mirror* m = new Mirror;
+        m->table = IsaTable::from_file(path);
+        m->flat = FlatTable::compile(m->table);
+        m->view = FlatView{m->flat.bucket_dir.data(), m->flat.cand.data(), m->flat.var.data(), m->flat.pieces.data(),
+                           m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
+        return m;
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void* mir_load_text(const char* text, uint64_t len) {
+    try {
+        Mirror* m = new Mirror;
+        m->table = IsaTable::from_json_text(std::string(text, len));
+        m->flat = FlatTable::compile(m->table);
+        m->view = FlatView{m->flat.bucket_dir.data(), m->flat.cand.data(), m->flat.var.data(), m->flat.pieces.data(),
+                           m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
+        return m;
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+void mir_free(void* h) { delete (Mirror*)h; }
+void mir_info(void* h, uint32_t* keys, uint32_t* groups, uint32_t* buckets, uint32_t* max_bucket, uint32_t* pieces) {
+    Mirror* m = (Mirror*)h;
+    *keys = m->flat.n_keys; *groups = (uint32_t)m->flat.meta.size(); *buckets = m->flat.n_buckets;
+    *max_bucket = m->flat.max_bucket; *pieces = (uint32_t)m->flat.pieces.size();
+}
+void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
+    const Mirror* m = (const Mirror*)h;
+    pfor(n, threads, [=](uint64_t b, uint64_t e) {
+        for (uint64_t i = b; i < e; ++i) {
+            uint32_t f, c, s[8];
+            decode_word(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3], &f, s, &c);
+            form[i] = (uint16_t)f; ctrl[i] = c;
+            for (int k = 0; k < 8; ++k) slots[(uint64_t)k * n + i] = s[k];
+        }
+    });
+}
+void mir_encode_batch(void* h, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl, uint64_t n, uint32_t* words, int threads) {
+    const Mirror* m = (const Mirror*)h;
+    pfor(n, threads, [=](uint64_t b, uint64_t e) {
+        for (uint64_t i = b; i < e; ++i) {
+            uint32_t s[8];
+            for (int k = 0; k < 8; ++k) s[k] = slots[(uint64_t)k * n + i];
+            encode_record(m->view, form[i], s, ctrl[i], &words[4 * i], &words[4 * i + 1], &words[4 * i + 2], &words[4 * i + 3]);
+        }
+    });
+}
+void mir_roundtrip_batch(void* h, const uint32_t* words, uint64_t n, uint8_t* status, int threads) {
+    const Mirror* m = (const Mirror*)h;
+    pfor(n, threads, [=](uint64_t b, uint64_t e) {
+        for (uint64_t i = b; i < e; ++i)
+            status[i] = (uint8_t)roundtrip_word(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+    });
+}
+void mir_synth_batch(void* h, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first, uint64_t n, uint32_t* words,
+                     uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
+    const Mirror* m = (const Mirror*)h;
+    SynthTables st = build_synth_tables(m->table, mix, seed);
+    SynthView g{st.cdf.data(), st.rank_first.data(), st.rank_count.data(), (uint32_t)st.cdf.size(), noise_ppm, seed};
+    pfor(n, threads, [=](uint64_t b, uint64_t e) {
+        for (uint64_t i = b; i < e; ++i) {
+            uint32_t f = FORM_NONE, c = 0, s[8] = {0}, w[4];
+            if (synth_record(m->view, g, first + i, &f, s, &c, w)) encode_record(m->view, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+            else c = ctrl_from_raw(w[0], w[3]);
+            memcpy(words + 4 * i, w, 16);
+            if (form) form[i] = (uint16_t)f;
+            if (ctrl) ctrl[i] = c;
+            if (slots) for (int k = 0; k < 8; ++k) slots[(uint64_t)k * n + i] = s[k];
+        }
+    });
+}
+}
