@@ -442,7 +442,7 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         ctx->by_name[{ft.meta[v].key, ft.meta[v].mod_group}] = (uint32_t)v;
         for (const FieldMeta& f : ft.meta[v].fields)
             ctx->field_infos[v].push_back(
-                cubit_field_info{f.shift, f.bits, f.token_idx, f.dst_pos, f.name.c_str(), f.extraction.c_str()});
+                cubit_field_info{f.shift, f.bits, f.token_idx, f.dst_pos, f.stored_bits, f.name.c_str(), f.extraction.c_str()});
     }
     for (int k = 0; k < n_devices; ++k) {
         std::unique_ptr<DeviceState> d(new DeviceState);
@@ -450,10 +450,14 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         cubit_ctx* c = nullptr;   // failures during creation report through the thread-local message
         CU_TRY(c, cudaSetDevice(d->device));
         CU_TRY(c, cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, d->device));
-        int rc = upload(c, d.get(), ft.bucket_dir, &d->view.bucket_dir);
-        if (!rc) rc = upload(c, d.get(), ft.cand, &d->view.cand);
+        int rc = upload(c, d.get(), ft.dir, &d->view.dir);
+        if (!rc) rc = upload(c, d.get(), ft.nodes, &d->view.nodes);
+        if (!rc) rc = upload(c, d.get(), ft.children, &d->view.children);
+        if (!rc) rc = upload(c, d.get(), ft.classes, &d->view.classes);
+        if (!rc) rc = upload(c, d.get(), ft.broad, &d->view.broad);
+        if (!rc) rc = upload(c, d.get(), ft.members, &d->view.members);
+        if (!rc) rc = upload(c, d.get(), ft.ext, &d->view.ext);
         if (!rc) rc = upload(c, d.get(), ft.var, &d->view.var);
-        if (!rc) rc = upload(c, d.get(), ft.pieces, &d->view.pieces);
         if (!rc) rc = upload(c, d.get(), ft.gfields, &d->view.gfields);
         if (rc) return rc;
         d->view.n_variants = (uint32_t)ft.meta.size();

@@ -634,30 +634,67 @@ struct Oracle {
 // Record layout: where the field values of a variant live in the 8 x u32 slots
 // ---------------------------------------------------------------------------------------
 
-// One slot per multi-bit field (two above 32 bits) with 1-bit fields sharing the next
-// slot(s); if that needs more than eight slots, fields are packed back to back.
-std::vector<uint32_t> slot_positions(const Entry& e) {
-    uint32_t multi = 0, ones = 0;
+// Only the part of a field below bit 96 is stored (the decoder never sees more).
+// Layout 0: multi-bit fields take slots from 0 in table order (two slots above 32 stored
+// bits); 1-bit fields share slot 7 at (source bit mod 32), rotated left by r1 for fields in
+// bits 63:32 and r2 for bits 95:64, (r1, r2) being the first pair in (0,0), (0,1), ... that
+// keeps the three groups apart.  Layout 1, when layout 0 does not fit (more than 8 slots,
+// flags with 8 multi-bit slots, two 1-bit fields on one bit, no rotation) or stored field
+// ranges overlap: every field stays at its position in the word.
+const uint32_t NOT_STORED = 0xFFFFFFFFu;
+struct Layout {
+    std::vector<uint32_t> pos, stored;
+    int kind;
+};
+uint32_t rotl32(uint32_t x, uint32_t r) { return r ? ((x << r) | (x >> (32 - r))) : x; }
+
+Layout slot_layout(const Entry& e) {
+    Layout L;
+    u128 used = 0;
+    bool overlap = false, dup = false;
+    uint32_t multi = 0, fm[3] = {0, 0, 0};
     for (const Field& f : e.fields) {
-        if (f.bits == 1) ++ones; else multi += f.bits > 32 ? 2 : 1;
+        uint32_t sb = f.shift >= 96 ? 0 : std::min<uint32_t>(f.shift + f.bits, 96) - f.shift;
+        L.stored.push_back(sb);
+        if (!sb) continue;
+        u128 r = ((((u128)1) << sb) - 1) << f.shift;
+        if (used & r) overlap = true;
+        used |= r;
+        if (sb == 1) {
+            if (fm[f.shift >> 5] >> (f.shift & 31) & 1) dup = true;
+            fm[f.shift >> 5] |= 1u << (f.shift & 31);
+        } else multi += sb > 32 ? 2 : 1;
     }
-    std::vector<uint32_t> pos;
-    if (multi + (ones + 31) / 32 <= 8) {
-        uint32_t slot = 0, flag = multi * 32;
-        for (const Field& f : e.fields) {
-            if (f.bits == 1) pos.push_back(flag++);
-            else { pos.push_back(slot * 32); slot += f.bits > 32 ? 2 : 1; }
+    const bool flags = fm[0] | fm[1] | fm[2];
+    uint32_t r1 = 0, r2 = 0;
+    bool rot_ok = !flags;
+    for (uint32_t a = 0; a < 32 && !rot_ok; ++a)
+        for (uint32_t b = 0; b < 32 && !rot_ok; ++b) {
+            uint32_t x = fm[0], y = rotl32(fm[1], a), z = rotl32(fm[2], b);
+            if (!(x & y) && !(x & z) && !(y & z)) { rot_ok = true; r1 = a; r2 = b; }
         }
-    } else {
-        uint32_t at = 0;
-        for (const Field& f : e.fields) { pos.push_back(at); at += f.bits; }
+    L.kind = (!overlap && !dup && rot_ok && multi + (flags ? 1 : 0) <= 8) ? 0 : 1;
+    uint32_t slot = 0;
+    for (size_t i = 0; i < e.fields.size(); ++i) {
+        const Field& f = e.fields[i];
+        const uint32_t sb = L.stored[i];
+        if (!sb) L.pos.push_back(NOT_STORED);
+        else if (L.kind == 1) L.pos.push_back(f.shift);
+        else if (sb == 1) {
+            const uint32_t limb = f.shift >> 5, r = limb == 0 ? 0 : (limb == 1 ? r1 : r2);
+            L.pos.push_back(224 + (((f.shift & 31) + r) & 31));
+        } else { L.pos.push_back(slot * 32); slot += sb > 32 ? 2 : 1; }
     }
-    return pos;
+    return L;
 }
 
+// Writes `nbits` of v at bit `pos` of the slot area, replacing what was there.
 void put_bits(uint32_t slots[8], uint32_t pos, uint32_t nbits, uint64_t v) {
-    for (uint32_t b = 0; b < nbits; ++b)
-        if ((v >> b) & 1) slots[(pos + b) >> 5] |= 1u << ((pos + b) & 31);
+    for (uint32_t b = 0; b < nbits; ++b) {
+        uint32_t& w = slots[(pos + b) >> 5];
+        const uint32_t bit = 1u << ((pos + b) & 31);
+        if ((v >> b) & 1) w |= bit; else w &= ~bit;
+    }
 }
 uint64_t get_bits(const uint32_t slots[8], uint32_t pos, uint32_t nbits) {
     uint64_t v = 0;
@@ -680,8 +717,9 @@ void decode_to_record(const Oracle& o, u128 code, uint16_t* form, uint32_t slots
     Decoded d = o.decode(code);
     for (int s = 0; s < 8; ++s) slots[s] = 0;
     if (d.status != 0) { *form = 0xFFFF; *ctrl = pack_ctrl(code, 0, false, (unsigned)d.status); return; }
-    std::vector<uint32_t> pos = slot_positions(*d.entry);
-    for (size_t i = 0; i < d.values.size(); ++i) put_bits(slots, pos[i], d.entry->fields[i].bits, d.values[i]);
+    Layout L = slot_layout(*d.entry);
+    for (size_t i = 0; i < d.values.size(); ++i)
+        if (L.pos[i] != NOT_STORED) put_bits(slots, L.pos[i], L.stored[i], d.values[i]);
     *form = (uint16_t)d.variant;
     *ctrl = pack_ctrl(code, d.synth, d.tie, 0);
 }
@@ -782,9 +820,10 @@ u128 encode_from_record(const Oracle& o, uint16_t form, const uint32_t slots[8],
     if (form >= o.by_variant.size()) return 0;
     const Candidate& c = *o.by_variant[form];
     const Entry& e = *o.table.get(c.key, c.mod_group);
-    std::vector<uint32_t> pos = slot_positions(e);
+    Layout L = slot_layout(e);
     std::vector<uint64_t> values;
-    for (size_t i = 0; i < e.fields.size(); ++i) values.push_back(get_bits(slots, pos[i], e.fields[i].bits));
+    for (size_t i = 0; i < e.fields.size(); ++i)
+        values.push_back(L.pos[i] == NOT_STORED ? 0 : get_bits(slots, L.pos[i], L.stored[i]));
     return orc_encode_record(o, form, values, (ctrl >> 24) & 0xF, (ctrl >> 20) & 0xF, (ctrl >> 17) & 7, ctrl & 0x1FFFF);
 }
 
@@ -892,7 +931,7 @@ u128 synth_word(const Oracle& o, const Mix& mix, uint64_t seed, uint32_t noise_p
     const unsigned wait = (rc >> 24) & 63, reuse3 = (rc >> 32) & 7;
     const unsigned sched = (wait << 11) | (rbar << 8) | (wbar << 5) | (yld << 4) | stall;
     std::vector<uint64_t> values;
-    std::vector<uint32_t> pos = slot_positions(e);
+    Layout L = slot_layout(e);
     for (size_t f = 0; f < e.fields.size(); ++f) {
         const Field& fd = e.fields[f];
         const uint64_t r = draw(seed, i, 8 + f);
@@ -906,8 +945,8 @@ u128 synth_word(const Oracle& o, const Mix& mix, uint64_t seed, uint32_t noise_p
         v &= fd.mask;
         if (fd.shift >= 96) v = 0;
         else if (fd.shift + fd.bits > 96 && 96 - fd.shift < 64) v &= (1ull << (96 - fd.shift)) - 1;
+        if (L.pos[f] != NOT_STORED) put_bits(slots, L.pos[f], L.stored[f], v);
         values.push_back(v);
-        put_bits(slots, pos[f], fd.bits, v);
     }
     *form = (uint16_t)variant;
     *ctrl = sched | (reuse3 << 17) | (guard << 20);

@@ -1,4 +1,5 @@
-"""ctypes access to the CPU oracle (oracle/cubit_oracle.cpp).  Test infrastructure only."""
+"""ctypes access to the CPU oracle (cubit_oracle.cpp).  Test infrastructure only: imported by the
+tests, the smoke check and the CPU-baseline leg of the benchmark, never by the product package."""
 from __future__ import annotations
 
 import ctypes as C
@@ -8,8 +9,8 @@ from pathlib import Path
 
 import numpy as np
 
-ROOT = Path(__file__).resolve().parent.parent
-ORACLE_DIR = ROOT / "oracle"
+ORACLE_DIR = Path(__file__).resolve().parent
+ROOT = ORACLE_DIR.parent
 ORACLE_SO = ORACLE_DIR / "_build" / "liboracle.so"
 TABLE = ROOT / "cubit_b200" / "tables" / "sm120.json"
 

@@ -37,7 +37,8 @@ void* mir_load(const char* path) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_file(path);
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.bucket_dir.data(), m->flat.cand.data(), m->flat.var.data(), m->flat.pieces.data(),
+        m->view = FlatView{m->flat.dir.data(), m->flat.nodes.data(), m->flat.children.data(), m->flat.classes.data(),
+                           m->flat.broad.data(), m->flat.members.data(), m->flat.ext.data(), m->flat.var.data(),
                            m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
@@ -47,16 +48,21 @@ void* mir_load_text(const char* text, uint64_t len) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_json_text(std::string(text, len));
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.bucket_dir.data(), m->flat.cand.data(), m->flat.var.data(), m->flat.pieces.data(),
+        m->view = FlatView{m->flat.dir.data(), m->flat.nodes.data(), m->flat.children.data(), m->flat.classes.data(),
+                           m->flat.broad.data(), m->flat.members.data(), m->flat.ext.data(), m->flat.var.data(),
                            m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
 void mir_free(void* h) { delete (Mirror*)h; }
-void mir_info(void* h, uint32_t* keys, uint32_t* groups, uint32_t* buckets, uint32_t* max_bucket, uint32_t* pieces) {
+// out[0..9]: keys, variants, buckets, largest bucket, nodes, child refs, leaves, classes, largest leaf, depth
+void mir_info(void* h, uint32_t* out) {
     Mirror* m = (Mirror*)h;
-    *keys = m->flat.n_keys; *groups = (uint32_t)m->flat.meta.size(); *buckets = m->flat.n_buckets;
-    *max_bucket = m->flat.max_bucket; *pieces = (uint32_t)m->flat.pieces.size();
+    const FlatTable& f = m->flat;
+    const uint32_t v[10] = {f.n_keys, (uint32_t)f.meta.size(), f.n_buckets, f.max_bucket, (uint32_t)(f.nodes.size() / NR_WORDS),
+                            (uint32_t)f.children.size(), f.n_leaves, (uint32_t)(f.classes.size() / CR_WORDS),
+                            f.max_leaf_classes, f.max_depth};
+    for (int i = 0; i < 10; ++i) out[i] = v[i];
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
     const Mirror* m = (const Mirror*)h;

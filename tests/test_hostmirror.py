@@ -1,0 +1,88 @@
+"""The per-word core the CUDA kernels are compiled from (csrc/codec_core.cuh), run as plain C++ over the
+host copy of the flat table, against the oracle.  Catches flat-table and rule-logic bugs without a GPU."""
+import ctypes as C
+import subprocess
+
+import numpy as np
+import pytest
+
+import cubit_b200
+from cubit_b200 import MIX_FAMILY, MIX_UNIFORM, MIX_ZIPF
+from test_gpu_parity import adversarial_words
+
+HERE = cubit_b200.build.PKG.parent / "tests" / "hostmirror"
+SO = HERE / "_build" / "libmirror.so"
+CSRC = cubit_b200.build.CSRC
+T = 8
+
+
+@pytest.fixture(scope="module")
+def mirror():
+    srcs = [HERE / "mirror.cpp", CSRC / "isa_table.cpp", CSRC / "flat_table.cpp"]
+    deps = srcs + [CSRC / "codec_core.cuh"]
+    if not SO.exists() or any(d.stat().st_mtime > SO.stat().st_mtime for d in deps):
+        SO.parent.mkdir(exist_ok=True)
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-Wno-unknown-pragmas", "-o", str(SO)]
+                       + [str(s) for s in srcs], check=True)
+    lib = C.CDLL(str(SO))
+    lib.mir_load.restype = C.c_void_p
+    lib.mir_load.argtypes = [C.c_char_p]
+    h = C.c_void_p(lib.mir_load(str(cubit_b200.build.PKG / "tables" / "sm120.json").encode()))
+    assert h
+
+    class M:
+        def decode(self, words):
+            n = len(words)
+            form = np.zeros(n, np.uint16); slots = np.zeros((8, n), np.uint32); ctrl = np.zeros(n, np.uint32)
+            lib.mir_decode_batch(h, C.c_void_p(words.ctypes.data), C.c_uint64(n), C.c_void_p(form.ctypes.data),
+                                 C.c_void_p(slots.ctypes.data), C.c_void_p(ctrl.ctypes.data), T)
+            return form, slots, ctrl
+
+        def encode(self, form, slots, ctrl):
+            n = len(form)
+            words = np.zeros((n, 16), np.uint8)
+            lib.mir_encode_batch(h, C.c_void_p(form.ctypes.data), C.c_void_p(slots.ctypes.data), C.c_void_p(ctrl.ctypes.data),
+                                 C.c_uint64(n), C.c_void_p(words.ctypes.data), T)
+            return words
+
+        def roundtrip(self, words):
+            st = np.zeros(len(words), np.uint8)
+            lib.mir_roundtrip_batch(h, C.c_void_p(words.ctypes.data), C.c_uint64(len(words)), C.c_void_p(st.ctypes.data), T)
+            return st
+
+        def synth(self, mix, seed, n, noise=0, first=0):
+            words = np.zeros((n, 16), np.uint8); form = np.zeros(n, np.uint16)
+            slots = np.zeros((8, n), np.uint32); ctrl = np.zeros(n, np.uint32)
+            lib.mir_synth_batch(h, mix, C.c_uint64(seed), noise, C.c_uint64(first), C.c_uint64(n), C.c_void_p(words.ctypes.data),
+                                C.c_void_p(form.ctypes.data), C.c_void_p(slots.ctypes.data), C.c_void_p(ctrl.ctypes.data), T)
+            return words, form, slots, ctrl
+    return M()
+
+
+@pytest.mark.parametrize("mix,seed,noise", [(MIX_UNIFORM, 0, 0), (MIX_ZIPF, 1, 0), (MIX_ZIPF, 7, 10000),
+                                            (MIX_FAMILY, 3, 0), (MIX_UNIFORM, 5, 500000)])
+def test_core_matches_oracle_on_streams(mirror, oracle, mix, seed, noise):
+    n = 100000
+    ow, of, os_, oc = oracle.synth(mix, seed, n, noise_ppm=noise, threads=T)
+    mw, mf, ms, mc = mirror.synth(mix, seed, n, noise)
+    assert (ow == mw).all() and (of == mf).all() and (os_ == ms).all() and (oc == mc).all()
+    od, md = oracle.decode_batch(ow, threads=T), mirror.decode(ow)
+    for a, b in zip(od, md):
+        assert (a == b).all()
+    assert (oracle.encode_batch(*od, threads=T) == mirror.encode(*md)).all()
+    assert (oracle.roundtrip_batch(ow, threads=T) == mirror.roundtrip(ow)).all()
+
+
+def test_core_matches_oracle_on_adversarial_words(mirror, oracle):
+    words = adversarial_words(np.random.default_rng(1), 30)
+    od, md = oracle.decode_batch(words, threads=T), mirror.decode(words)
+    for a, b in zip(od, md):
+        assert (a == b).all()
+    assert len(set(od[0].tolist())) > 1200          # the inputs reach most of the table
+    assert (oracle.roundtrip_batch(words, threads=T) == mirror.roundtrip(words)).all()
+    rng = np.random.default_rng(3)
+    form = np.repeat(np.arange(2872, dtype=np.uint16), 10)
+    slots = rng.integers(0, 2**32, size=(8, len(form)), dtype=np.uint32)
+    ctrl = rng.integers(0, 2**32, size=len(form), dtype=np.uint32)
+    form[::97] = 0xFFFF
+    assert (oracle.encode_batch(form, slots, ctrl, threads=T) == mirror.encode(form, slots, ctrl)).all()
