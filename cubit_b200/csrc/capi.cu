@@ -2,9 +2,11 @@
 //
 // Kernels are one thread per instruction word over a grid-stride loop.  A warp reads 32
 // consecutive 16-byte words (512 contiguous bytes) and writes 32 consecutive entries of
-// every output plane, so all global traffic is coalesced; the flat ISA table (about 300 KB)
-// stays in L1/L2 through the read-only path while the stream itself is loaded and stored
-// with streaming hints.
+// every output plane, so all global traffic is coalesced and uses streaming hints.  The
+// per-word table lookups are data dependent and diverge between lanes, so the hot part of
+// the ISA table (about 217 KB) is staged into shared memory once per CTA by persistent
+// CTAs (one per SM, 1024 threads); small batches use a variant that reads the table through
+// the read-only global path instead of paying for the staging.
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
@@ -18,6 +20,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/cubit_b200.h"
@@ -32,11 +35,32 @@ using namespace cubit;
 
 namespace {
 
-constexpr int kBlock = 256;
+constexpr int kBlock = 256;          // table in global memory
+constexpr int kBlockShared = 1024;   // table staged in shared memory, one CTA per SM
+constexpr uint64_t kSharedMinWords = 1u << 17;   // below this the staging copy is not worth it
 enum { CNT_DECODED = 0, CNT_REJECTED, CNT_TIE, CNT_EXACT, CNT_MISMATCH, CNT_WORDS };
 
-// Adds per-thread 0/1 tallies into the launch's counters: warp reduce, then one shared
-// atomic per warp, then one global atomic per block.
+extern __shared__ uint4 g_table_smem[];
+
+// Gives the view the kernel works with: for HotShared the hot part of the blob is first
+// copied into dynamic shared memory by the whole CTA.
+template <class HOT>
+__device__ __forceinline__ FlatView stage_table(const FlatView& t) {
+    return t;
+}
+template <>
+__device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t) {
+    const uint4* src = reinterpret_cast<const uint4*>(t.cold);
+    const uint32_t quads = t.at.hot_words / 4;
+    for (uint32_t i = threadIdx.x; i < quads; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
+    __syncthreads();
+    FlatView v = t;
+    v.hot = reinterpret_cast<const uint32_t*>(g_table_smem);
+    return v;
+}
+
+// Adds per-thread tallies into the launch's counters: warp reduce, then one shared atomic
+// per warp, then one global atomic per block.
 template <int N>
 __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int (&which)[N],
                                             unsigned long long* counters) {
@@ -53,16 +77,18 @@ __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int
         atomicAdd(&counters[threadIdx.x], (unsigned long long)s_acc[threadIdx.x]);
 }
 
-__global__ void __launch_bounds__(kBlock)
-decode_kernel(FlatView t, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
+template <class HOT>
+__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
+    const FlatView t = stage_table<HOT>(tg);
     uint32_t tally[3] = {0, 0, 0};
-    const uint64_t step = (uint64_t)gridDim.x * kBlock;
-    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         const uint4 w = __ldcs(words + i);
         uint32_t f, c, s[8];
-        decode_word(t, w.x, w.y, w.z, w.w, &f, s, &c);
+        decode_word<HOT>(t, w.x, w.y, w.z, w.w, &f, s, &c);
         __stcs(form + i, (uint16_t)f);
 #pragma unroll
         for (int k = 0; k < 8; ++k) __stcs(slots + (uint64_t)k * slot_stride + i, s[k]);
@@ -76,28 +102,32 @@ decode_kernel(FlatView t, const uint4* __restrict__ words, uint64_t n, uint16_t*
     }
 }
 
-__global__ void __launch_bounds__(kBlock)
-encode_kernel(FlatView t, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
+template <class HOT>
+__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
               uint64_t slot_stride, const uint32_t* __restrict__ ctrl, uint64_t n, uint4* __restrict__ words) {
-    const uint64_t step = (uint64_t)gridDim.x * kBlock;
-    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+    const FlatView t = stage_table<HOT>(tg);
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         uint32_t s[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) s[k] = __ldcs(slots + (uint64_t)k * slot_stride + i);
         uint4 w;
-        encode_record(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
+        encode_record<HOT>(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
         __stcs(words + i, w);
     }
 }
 
-__global__ void __launch_bounds__(kBlock)
-roundtrip_kernel(FlatView t, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
+template <class HOT>
+__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
+    const FlatView t = stage_table<HOT>(tg);
     uint32_t tally[3] = {0, 0, 0};
-    const uint64_t step = (uint64_t)gridDim.x * kBlock;
-    for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         const uint4 w = __ldcs(words + i);
-        const uint32_t st = roundtrip_word(t, w.x, w.y, w.z, w.w);
+        const uint32_t st = roundtrip_word<HOT>(t, w.x, w.y, w.z, w.w);
         __stcs(status + i, (uint8_t)st);
         tally[0] += st == RT_EXACT; tally[1] += st == RT_MISMATCH; tally[2] += st == RT_REJECTED;
     }
@@ -114,7 +144,7 @@ synth_kernel(FlatView t, SynthView g, uint64_t first, uint64_t n, uint4* __restr
     const uint64_t step = (uint64_t)gridDim.x * kBlock;
     for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
         uint32_t f = FORM_NONE, c = 0, s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, w[4];
-        if (synth_record(t, g, first + i, &f, s, &c, w)) encode_record(t, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+        if (synth_record(t, g, first + i, &f, s, &c, w)) encode_record<HotGlobal>(t, f, s, c, &w[0], &w[1], &w[2], &w[3]);
         else c = ctrl_from_raw(w[0], w[3]);
         if (words) words[i] = make_uint4(w[0], w[1], w[2], w[3]);
         if (form) form[i] = (uint16_t)f;
@@ -131,6 +161,8 @@ thread_local std::string g_create_error;
 struct DeviceState {
     int device = -1;
     int sm_count = 0;
+    bool shared_ok = false;   // the hot part of the table fits the opt-in shared memory of this device
+    uint32_t hot_bytes = 0;
     FlatView view{};
     std::vector<void*> table_allocs;
     unsigned long long* counters = nullptr;   // kCounterSlots x CNT_WORDS
@@ -211,6 +243,34 @@ int grid_for(const DeviceState* d, uint64_t n) {
     const uint64_t blocks = (n + kBlock - 1) / kBlock;
     const uint64_t cap = (uint64_t)d->sm_count * 8;   // whole waves of resident blocks
     return (int)std::max<uint64_t>(1, std::min(blocks, cap));
+}
+
+// Large batches run on persistent CTAs with the table in shared memory.
+bool use_shared(const DeviceState* d, uint64_t n) { return d->shared_ok && n >= kSharedMinWords; }
+int grid_shared(const DeviceState* d, uint64_t n) {
+    return (int)std::max<uint64_t>(1, std::min<uint64_t>((n + kBlockShared - 1) / kBlockShared, (uint64_t)d->sm_count));
+}
+
+void launch_decode(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint16_t* form, uint32_t* slots,
+                   uint64_t stride, uint32_t* ctrl, unsigned long long* dc) {
+    if (use_shared(d, n))
+        decode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+    else
+        decode_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+}
+void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, const uint32_t* slots, uint64_t stride,
+                   const uint32_t* ctrl, uint64_t n, uint4* words) {
+    if (use_shared(d, n))
+        encode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, form, slots, stride, ctrl, n, words);
+    else
+        encode_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, form, slots, stride, ctrl, n, words);
+}
+void launch_roundtrip(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint8_t* status,
+                      unsigned long long* dc) {
+    if (use_shared(d, n))
+        roundtrip_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, status, dc);
+    else
+        roundtrip_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, status, dc);
 }
 
 DeviceState* device_of_pointer(cubit_ctx* ctx, const void* p) {
@@ -295,9 +355,8 @@ int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint
         const uint64_t m = std::min(chunk, end - at);
         CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
         rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
-            decode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, (uint16_t*)(st + o_form),
-                                                                     (uint32_t*)(st + o_slots), chunk,
-                                                                     (uint32_t*)(st + o_ctrl), dc);
+            launch_decode(d, d->stream, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), chunk,
+                          (uint32_t*)(st + o_ctrl), dc);
         });
         if (rc) return rc;
         CU_TRY(ctx, cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
@@ -327,9 +386,8 @@ int encode_host_range(cubit_ctx* ctx, DeviceState* d, const uint16_t* form, cons
             CU_TRY(ctx, cudaMemcpyAsync(st + o_slots + (uint64_t)k * chunk * 4, slots + (uint64_t)k * n_total + at, m * 4,
                                         cudaMemcpyHostToDevice, d->stream));
         CU_TRY(ctx, cudaMemcpyAsync(st + o_ctrl, ctrl + at, m * 4, cudaMemcpyHostToDevice, d->stream));
-        encode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint16_t*)(st + o_form),
-                                                                 (const uint32_t*)(st + o_slots), chunk,
-                                                                 (const uint32_t*)(st + o_ctrl), m, (uint4*)st);
+        launch_encode(d, d->stream, (const uint16_t*)(st + o_form), (const uint32_t*)(st + o_slots), chunk,
+                      (const uint32_t*)(st + o_ctrl), m, (uint4*)st);
         CU_TRY(ctx, cudaGetLastError());
         CU_TRY(ctx, cudaMemcpyAsync(words + at * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
         CU_TRY(ctx, cudaStreamSynchronize(d->stream));
@@ -350,7 +408,7 @@ int roundtrip_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, u
         const uint64_t m = std::min(chunk, end - at);
         CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
         rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
-            roundtrip_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, st + o_status, dc);
+            launch_roundtrip(d, d->stream, (const uint4*)st, m, st + o_status, dc);
         });
         if (rc) return rc;
         CU_TRY(ctx, cudaMemcpyAsync(status + at, st + o_status, m, cudaMemcpyDeviceToHost, d->stream));
@@ -450,17 +508,19 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         cubit_ctx* c = nullptr;   // failures during creation report through the thread-local message
         CU_TRY(c, cudaSetDevice(d->device));
         CU_TRY(c, cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, d->device));
-        int rc = upload(c, d.get(), ft.dir, &d->view.dir);
-        if (!rc) rc = upload(c, d.get(), ft.nodes, &d->view.nodes);
-        if (!rc) rc = upload(c, d.get(), ft.children, &d->view.children);
-        if (!rc) rc = upload(c, d.get(), ft.classes, &d->view.classes);
-        if (!rc) rc = upload(c, d.get(), ft.broad, &d->view.broad);
-        if (!rc) rc = upload(c, d.get(), ft.members, &d->view.members);
-        if (!rc) rc = upload(c, d.get(), ft.ext, &d->view.ext);
-        if (!rc) rc = upload(c, d.get(), ft.var, &d->view.var);
-        if (!rc) rc = upload(c, d.get(), ft.gfields, &d->view.gfields);
+        const uint32_t* blob = nullptr;
+        int rc = upload(c, d.get(), ft.blob, &blob);
         if (rc) return rc;
-        d->view.n_variants = (uint32_t)ft.meta.size();
+        d->view.hot = blob; d->view.cold = blob; d->view.at = ft.at;
+        d->hot_bytes = ft.at.hot_words * 4;
+        int optin = 0;
+        CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
+        d->shared_ok = (int)d->hot_bytes + 1024 <= optin;
+        if (d->shared_ok) {
+            CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+            CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+            CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        }
         CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
         for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
         CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
@@ -558,7 +618,7 @@ extern "C" int cubit_decode_batch(cubit_ctx* ctx, const void* words, uint64_t n,
         CU_TRY(ctx, cudaSetDevice(d->device));
         cudaStream_t s = (cudaStream_t)stream;
         return run_counted(ctx, d, s, counts, [&](unsigned long long* dc) {
-            decode_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, (const uint4*)words, n, form, slots, n, ctrl, dc);
+            launch_decode(d, s, (const uint4*)words, n, form, slots, n, ctrl, dc);
         });
     }
     if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
@@ -583,7 +643,7 @@ extern "C" int cubit_encode_batch(cubit_ctx* ctx, const uint16_t* form, const ui
         if ((uintptr_t)words % 16) return fail(ctx, CUBIT_ERR_INVALID, "device words must be 16-byte aligned");
         CU_TRY(ctx, cudaSetDevice(d->device));
         cudaStream_t s = (cudaStream_t)stream;
-        encode_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, form, slots, n, ctrl, n, (uint4*)words);
+        launch_encode(d, s, form, slots, n, ctrl, n, (uint4*)words);
         CU_TRY(ctx, cudaGetLastError());
         return CUBIT_OK;
     }
@@ -611,7 +671,7 @@ extern "C" int cubit_roundtrip_batch(cubit_ctx* ctx, const void* words, uint64_t
         CU_TRY(ctx, cudaSetDevice(d->device));
         cudaStream_t s = (cudaStream_t)stream;
         return run_counted(ctx, d, s, counts, [&](unsigned long long* dc) {
-            roundtrip_kernel<<<grid_for(d, n), kBlock, 0, s>>>(d->view, (const uint4*)words, n, status, dc);
+            launch_roundtrip(d, s, (const uint4*)words, n, status, dc);
         });
     }
     if (mem_kind != CUBIT_MEM_HOST) return fail(ctx, CUBIT_ERR_INVALID, "unknown mem_kind");
@@ -772,8 +832,8 @@ extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint
             CU_TRY(ctx, cudaMemcpyAsync(st + (lo - b) * 16, src, (hi - lo) * 16, cudaMemcpyHostToDevice, d->stream));
         }
         rc = run_counted(ctx, d, d->stream, part, [&](unsigned long long* dc) {
-            decode_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, (const uint4*)st, m, (uint16_t*)(st + o_form),
-                                                                     (uint32_t*)(st + o_slots), m, (uint32_t*)(st + o_ctrl), dc);
+            launch_decode(d, d->stream, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), m,
+                          (uint32_t*)(st + o_ctrl), dc);
         });
         if (rc) return rc;
         CU_TRY(ctx, cudaMemcpyAsync(form + b, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));

@@ -182,24 +182,31 @@ struct TreeBuilder {
             std::sort(mem.begin(), mem.end(), [&](uint32_t a, uint32_t b) { return st[a].key < st[b].key; });
             if (mem.size() > 255) throw std::runtime_error("class too large");
             const Static& best = st[mem[0]];
-            uint32_t rec[CR_WORDS] = {0};
+            uint32_t rec[CR_WORDS] = {0}, extra[CX_WORDS] = {0};
             for (int k = 0; k < 3; ++k) {
                 // A side that can never match gets mask 0 / base 1: (cc & 0) ^ 1 is never 0.
                 rec[CR_SMASK + k] = best.s_ok ? uint32_t(best.smask >> (32 * k)) : 0;
                 rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 1u : 0u);
-                rec[CR_BASE + k] = uint32_t(best.base96 >> (32 * k));
+                extra[k] = uint32_t(best.base96 >> (32 * k));
             }
             uint32_t info = uint32_t(mem.size()) << CI_MEMBERS_POS;
             // The broad test only adds something when it can succeed where the strict one fails.
             if (best.b_ok && !(best.s_ok && best.bmask == best.smask)) {
                 const uint32_t bi = uint32_t(ft.broad.size() / BR_WORDS);
-                if (bi > 0xFFFF) throw std::runtime_error("too many broad records");
+                if (bi > CI_BROAD_MASK) throw std::runtime_error("too many broad records");
                 uint32_t br[BR_WORDS] = {0};
                 for (int k = 0; k < 3; ++k) { br[k] = uint32_t(best.bmask >> (32 * k)); br[3 + k] = uint32_t(best.bbase >> (32 * k)); }
                 ft.broad.insert(ft.broad.end(), br, br + BR_WORDS);
                 info |= bi | CI_HAS_BROAD;
             }
             if (mem.size() > 1 && (st[mem[1]].key >> KEY_TUPLE_SHIFT) == (best.key >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
+            // popcount(and_base & cc) on a strict match: the part under the mask is constant.
+            if (best.s_ok) {
+                info |= uint32_t(popcount128(best.base96 & best.smask)) << CI_POPC_POS;
+                if (best.base96 & ~best.smask) info |= CI_DYN_POPC;
+            } else {
+                info |= CI_DYN_POPC;
+            }
             rec[CR_INFO] = info;
             rec[CR_MEMBERS] = uint32_t(ft.members.size() / MR_WORDS);
             rec[CR_FIRST_FLAGS] = best.flags;
@@ -214,6 +221,7 @@ struct TreeBuilder {
             }
             rec[CR_ANY_FLAGS] = any;
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
+            ft.class_extra.insert(ft.class_extra.end(), extra, extra + CX_WORDS);
         }
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
@@ -565,15 +573,41 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         ft.max_bucket = std::max(ft.max_bucket, ++bucket_size[b]);
         if (st[vi].matchable()) buckets[b].push_back(uint32_t(vi));
     }
-    ft.dir.assign(4096, REF_NONE);
+    std::vector<uint32_t> dir16(2048, 0), bucket_ref;
     TreeBuilder tb{st, ft};
     for (size_t b = 0; b < 4096; ++b) {
         if (!bucket_size[b]) continue;
         ++ft.n_buckets;
-        ft.dir[b] = buckets[b].empty() ? uint32_t(REF_LEAF) : tb.build(buckets[b], 0xFFF, 0);
+        bucket_ref.push_back(buckets[b].empty() ? uint32_t(REF_LEAF) : tb.build(buckets[b], 0xFFF, 0));
+        dir16[b >> 1] |= uint32_t(bucket_ref.size()) << (16 * (b & 1));
     }
     ft.max_depth = tb.max_depth;
     if (ft.broad.empty()) ft.broad.assign(BR_WORDS, 0);
+
+    // One blob: hot sections first, each 16-byte aligned.
+    auto place = [&](const std::vector<uint32_t>& src) {
+        while (ft.blob.size() % 4) ft.blob.push_back(0);
+        const uint32_t at = uint32_t(ft.blob.size());
+        ft.blob.insert(ft.blob.end(), src.begin(), src.end());
+        return at;
+    };
+    BlobLayout& L = ft.at;
+    L.dir16 = place(dir16);
+    L.bucket_ref = place(bucket_ref);
+    L.nodes = place(ft.nodes);
+    L.children = place(ft.children);
+    L.classes = place(ft.classes);
+    L.broad = place(ft.broad);
+    L.ext = place(ft.ext);
+    while (ft.blob.size() % 4) ft.blob.push_back(0);
+    L.hot_words = uint32_t(ft.blob.size());
+    L.class_extra = place(ft.class_extra);
+    L.members = place(ft.members);
+    L.var = place(ft.var);
+    L.gfields = place(ft.gfields);
+    while (ft.blob.size() % 4) ft.blob.push_back(0);
+    L.total_words = uint32_t(ft.blob.size());
+    L.n_variants = uint32_t(nv);
     return ft;
 }
 

@@ -5,6 +5,7 @@
 #include <string>
 #include <vector>
 
+#include "codec_core.cuh"
 #include "isa_table.hpp"
 
 namespace cubit {
@@ -29,10 +30,13 @@ struct VariantMeta {
 };
 
 struct FlatTable {
-    std::vector<uint32_t> dir;       // 4096 refs
+    std::vector<uint32_t> blob;      // every table, hot sections first; offsets in `at`
+    BlobLayout at{};
+    // Sections as built (kept for inspection; the kernels read the blob).
     std::vector<uint32_t> nodes;     // NR_WORDS each
     std::vector<uint32_t> children;  // refs
     std::vector<uint32_t> classes;   // CR_WORDS each
+    std::vector<uint32_t> class_extra;  // CX_WORDS each
     std::vector<uint32_t> broad;     // BR_WORDS each
     std::vector<uint32_t> members;   // MR_WORDS each
     std::vector<uint32_t> ext;       // XR_WORDS per variant

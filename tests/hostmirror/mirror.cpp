@@ -37,9 +37,7 @@ void* mir_load(const char* path) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_file(path);
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.dir.data(), m->flat.nodes.data(), m->flat.children.data(), m->flat.classes.data(),
-                           m->flat.broad.data(), m->flat.members.data(), m->flat.ext.data(), m->flat.var.data(),
-                           m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
+        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -48,28 +46,27 @@ void* mir_load_text(const char* text, uint64_t len) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_json_text(std::string(text, len));
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.dir.data(), m->flat.nodes.data(), m->flat.children.data(), m->flat.classes.data(),
-                           m->flat.broad.data(), m->flat.members.data(), m->flat.ext.data(), m->flat.var.data(),
-                           m->flat.gfields.data(), (uint32_t)m->flat.meta.size()};
+        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
 void mir_free(void* h) { delete (Mirror*)h; }
-// out[0..9]: keys, variants, buckets, largest bucket, nodes, child refs, leaves, classes, largest leaf, depth
+// out[0..9]: keys, variants, buckets, largest bucket, nodes, child refs, leaves, classes, largest leaf, depth;
+// out[10..11]: hot bytes, total bytes of the table blob
 void mir_info(void* h, uint32_t* out) {
     Mirror* m = (Mirror*)h;
     const FlatTable& f = m->flat;
-    const uint32_t v[10] = {f.n_keys, (uint32_t)f.meta.size(), f.n_buckets, f.max_bucket, (uint32_t)(f.nodes.size() / NR_WORDS),
+    const uint32_t v[12] = {f.n_keys, (uint32_t)f.meta.size(), f.n_buckets, f.max_bucket, (uint32_t)(f.nodes.size() / NR_WORDS),
                             (uint32_t)f.children.size(), f.n_leaves, (uint32_t)(f.classes.size() / CR_WORDS),
-                            f.max_leaf_classes, f.max_depth};
-    for (int i = 0; i < 10; ++i) out[i] = v[i];
+                            f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
+    for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
     const Mirror* m = (const Mirror*)h;
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; ++i) {
             uint32_t f, c, s[8];
-            decode_word(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3], &f, s, &c);
+            decode_word<HotPlain>(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3], &f, s, &c);
             form[i] = (uint16_t)f; ctrl[i] = c;
             for (int k = 0; k < 8; ++k) slots[(uint64_t)k * n + i] = s[k];
         }
@@ -81,7 +78,7 @@ void mir_encode_batch(void* h, const uint16_t* form, const uint32_t* slots, cons
         for (uint64_t i = b; i < e; ++i) {
             uint32_t s[8];
             for (int k = 0; k < 8; ++k) s[k] = slots[(uint64_t)k * n + i];
-            encode_record(m->view, form[i], s, ctrl[i], &words[4 * i], &words[4 * i + 1], &words[4 * i + 2], &words[4 * i + 3]);
+            encode_record<HotPlain>(m->view, form[i], s, ctrl[i], &words[4 * i], &words[4 * i + 1], &words[4 * i + 2], &words[4 * i + 3]);
         }
     });
 }
@@ -89,7 +86,7 @@ void mir_roundtrip_batch(void* h, const uint32_t* words, uint64_t n, uint8_t* st
     const Mirror* m = (const Mirror*)h;
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; ++i)
-            status[i] = (uint8_t)roundtrip_word(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+            status[i] = (uint8_t)roundtrip_word<HotPlain>(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
     });
 }
 void mir_synth_batch(void* h, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first, uint64_t n, uint32_t* words,
@@ -100,7 +97,7 @@ void mir_synth_batch(void* h, uint32_t mix, uint64_t seed, uint32_t noise_ppm, u
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; ++i) {
             uint32_t f = FORM_NONE, c = 0, s[8] = {0}, w[4];
-            if (synth_record(m->view, g, first + i, &f, s, &c, w)) encode_record(m->view, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+            if (synth_record(m->view, g, first + i, &f, s, &c, w)) encode_record<HotPlain>(m->view, f, s, c, &w[0], &w[1], &w[2], &w[3]);
             else c = ctrl_from_raw(w[0], w[3]);
             memcpy(words + 4 * i, w, 16);
             if (form) form[i] = (uint16_t)f;
