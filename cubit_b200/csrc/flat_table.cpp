@@ -149,13 +149,13 @@ struct Static {
     std::tuple<int, int, int, int, int> mid;   // opaque, plain-address, undiscovered, length, -score
     std::tuple<int, int> lo;                   // -popcount(match), -len(mod_group)
     uint32_t flags = 0;
-    uint64_t key = 0;                          // static rank key (filled after ranking)
     u128 weakest() const { return b_ok ? bmask : smask; }
     bool matchable() const { return s_ok || b_ok; }
 };
 
 struct TreeBuilder {
     const std::vector<Static>& st;
+    const std::vector<uint32_t>& ext_of;   // variant -> extraction record index
     FlatTable& ft;
     uint32_t max_depth = 0;
 
@@ -166,8 +166,29 @@ struct TreeBuilder {
         return ClassKey(s.s_ok, s.s_ok ? s.smask : 0, s.s_ok ? s.sbase : 0, s.b_ok, s.b_ok ? s.bmask : 0,
                         s.b_ok ? s.bbase : 0, s.base96);
     }
+    size_t class_count(const std::vector<uint32_t>& vs) const {
+        std::map<ClassKey, int> seen;
+        for (uint32_t v : vs) seen[class_key(v)] = 1;
+        return seen.size();
+    }
 
     uint32_t make_leaf(const std::vector<uint32_t>& vs) {
+        // Rank keys are dense inside the leaf: only its candidates are ever compared.
+        std::map<std::tuple<int, int, int, int, int>, uint32_t> mid_rank;
+        std::map<std::tuple<int, int>, uint32_t> lo_rank;
+        for (uint32_t v : vs) { mid_rank[st[v].mid] = 0; lo_rank[st[v].lo] = 0; }
+        uint32_t r = 0;
+        for (auto& kv : mid_rank) kv.second = r++;
+        r = 0;
+        for (auto& kv : lo_rank) kv.second = r++;
+        if (mid_rank.size() > 128 || lo_rank.size() > 128 || vs.size() > 256)
+            throw std::runtime_error("a leaf of the match tree has too many candidates for 32-bit rank keys");
+        std::map<uint32_t, uint32_t> key_of;   // variant -> static key; vs is in canonical order
+        for (size_t i = 0; i < vs.size(); ++i) {
+            const Static& s = st[vs[i]];
+            key_of[vs[i]] = (uint32_t(s.score < 0 ? 1 : 0) << 31) | (mid_rank[s.mid] << 22) | (lo_rank[s.lo] << 8) | uint32_t(i);
+        }
+
         std::map<ClassKey, std::vector<uint32_t>> groups;
         std::vector<ClassKey> order;   // classes in order of their first (canonical) member
         for (uint32_t v : vs) {
@@ -179,7 +200,7 @@ struct TreeBuilder {
         if (order.size() > 255 || first_class + order.size() >= (1u << 20)) throw std::runtime_error("leaf too large");
         for (const ClassKey& ck : order) {
             std::vector<uint32_t>& mem = groups[ck];
-            std::sort(mem.begin(), mem.end(), [&](uint32_t a, uint32_t b) { return st[a].key < st[b].key; });
+            std::sort(mem.begin(), mem.end(), [&](uint32_t a, uint32_t b) { return key_of[a] < key_of[b]; });
             if (mem.size() > 255) throw std::runtime_error("class too large");
             const Static& best = st[mem[0]];
             uint32_t rec[CR_WORDS] = {0}, extra[CX_WORDS] = {0};
@@ -187,8 +208,9 @@ struct TreeBuilder {
                 // A side that can never match gets mask 0 / base 1: (cc & 0) ^ 1 is never 0.
                 rec[CR_SMASK + k] = best.s_ok ? uint32_t(best.smask >> (32 * k)) : 0;
                 rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 1u : 0u);
-                extra[k] = uint32_t(best.base96 >> (32 * k));
+                extra[CX_BASE + k] = uint32_t(best.base96 >> (32 * k));
             }
+            extra[CX_MEMBERS] = uint32_t(ft.members.size() / MR_WORDS);
             uint32_t info = uint32_t(mem.size()) << CI_MEMBERS_POS;
             // The broad test only adds something when it can succeed where the strict one fails.
             if (best.b_ok && !(best.s_ok && best.bmask == best.smask)) {
@@ -199,25 +221,30 @@ struct TreeBuilder {
                 ft.broad.insert(ft.broad.end(), br, br + BR_WORDS);
                 info |= bi | CI_HAS_BROAD;
             }
-            if (mem.size() > 1 && (st[mem[1]].key >> KEY_TUPLE_SHIFT) == (best.key >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
-            // popcount(and_base & cc) on a strict match: the part under the mask is constant.
+            if (mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
+            // popcount(and_base & cc) on a strict match: the part under the mask is constant,
+            // the rest (typically baked guard bits) usually sits in one limb.
             if (best.s_ok) {
                 info |= uint32_t(popcount128(best.base96 & best.smask)) << CI_POPC_POS;
-                if (best.base96 & ~best.smask) info |= CI_DYN_POPC;
+                const u128 dyn = best.base96 & ~best.smask;
+                int limbs = 0, which = 0;
+                for (int k = 0; k < 3; ++k)
+                    if (uint32_t(dyn >> (32 * k))) { ++limbs; which = k; }
+                if (limbs == 1) { info |= uint32_t(which + 1) << CI_DYN_POS; rec[CR_DYN_MASK] = uint32_t(dyn >> (32 * which)); }
+                else if (limbs > 1) info |= 4u << CI_DYN_POS;
             } else {
-                info |= CI_DYN_POPC;
+                info |= 4u << CI_DYN_POS;
             }
             rec[CR_INFO] = info;
-            rec[CR_MEMBERS] = uint32_t(ft.members.size() / MR_WORDS);
             rec[CR_FIRST_FLAGS] = best.flags;
-            rec[CR_KEY_LO] = uint32_t(best.key);
-            rec[CR_KEY_HI] = uint32_t(best.key >> 32);
+            rec[CR_KEY] = key_of[mem[0]];
+            rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
             uint32_t any = 0;
             for (uint32_t v : mem) {
                 any |= st[v].flags & 0xFFFFu;
-                ft.members.push_back(uint32_t(st[v].key));
-                ft.members.push_back(uint32_t(st[v].key >> 32));
+                ft.members.push_back(key_of[v]);
                 ft.members.push_back(st[v].flags);
+                ft.members.push_back(v | (ext_of[v] << 16));
             }
             rec[CR_ANY_FLAGS] = any;
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
@@ -232,8 +259,8 @@ struct TreeBuilder {
         return uint32_t(x) ^ cb_rotl(uint32_t(x >> 32), r1) ^ cb_rotl(uint32_t(x >> 64), r2);
     }
 
-    // Splits `vs` on the mask bits that all of them check (beyond `used`); recursion ends in
-    // leaves whose members share no further discriminating bit.
+    // Splits `vs` on the mask bits that all of them check (beyond `used`), then on single
+    // bits that most of them check; recursion ends in leaves that no bit shrinks further.
     uint32_t build(const std::vector<uint32_t>& vs, u128 used, uint32_t depth) {
         max_depth = std::max(max_depth, depth);
         u128 common = (((u128)1) << 96) - 1;
@@ -242,47 +269,84 @@ struct TreeBuilder {
         std::map<u128, std::vector<uint32_t>> parts;
         if (vs.size() > 1 && common)
             for (uint32_t v : vs) parts[st[v].base96 & common].push_back(v);
-        if (parts.size() <= 1) return make_leaf(vs);
-
-        // Perfect hash of the masked word into a power-of-two child table.
-        uint32_t bits = 1;
-        while ((1u << bits) < parts.size()) ++bits;
-        uint32_t mult = 0, r1 = 0, r2 = 0;
-        bool ok = false;
-        uint64_t rng = 0x243F6A8885A308D3ull ^ (uint64_t(vs[0]) << 20) ^ depth;
-        for (uint32_t extra = 0; extra < 3 && !ok; ++extra) {
-            const uint32_t k = bits + extra;
-            for (uint32_t attempt = 0; attempt < 4000 && !ok; ++attempt) {
-                rng = splitmix64(rng);
-                const uint32_t m = uint32_t(rng) | 1u;
-                const uint32_t a = (attempt / 64) % 32, b = (attempt / 7) % 32;
-                std::vector<char> seen(1u << k, 0);
-                bool clash = false;
-                for (const auto& kv : parts) {
-                    const uint32_t h = (fold(kv.first, a, b) * m) >> (32 - k);
-                    if (seen[h]) { clash = true; break; }
-                    seen[h] = 1;
+        if (parts.size() > 1) {
+            // Perfect hash of the masked word into a power-of-two child table.
+            uint32_t bits = 1;
+            while ((1u << bits) < parts.size()) ++bits;
+            uint32_t mult = 0, r1 = 0, r2 = 0;
+            bool ok = false;
+            uint64_t rng = 0x243F6A8885A308D3ull ^ (uint64_t(vs[0]) << 20) ^ depth;
+            for (uint32_t extra = 0; extra < 3 && !ok; ++extra) {
+                const uint32_t k = bits + extra;
+                for (uint32_t attempt = 0; attempt < 4000 && !ok; ++attempt) {
+                    rng = splitmix64(rng);
+                    const uint32_t m = uint32_t(rng) | 1u;
+                    const uint32_t a = (attempt / 64) % 32, b = (attempt / 7) % 32;
+                    std::vector<char> seen(size_t(1) << k, 0);
+                    bool clash = false;
+                    for (const auto& kv : parts) {
+                        const uint32_t h = (fold(kv.first, a, b) * m) >> (32 - k);
+                        if (seen[h]) { clash = true; break; }
+                        seen[h] = 1;
+                    }
+                    if (!clash) { ok = true; mult = m; r1 = a; r2 = b; bits = k; }
                 }
-                if (!clash) { ok = true; mult = m; r1 = a; r2 = b; bits = k; }
+            }
+            if (ok) {
+                const uint32_t node = uint32_t(ft.nodes.size() / NR_WORDS);
+                ft.nodes.resize(ft.nodes.size() + NR_WORDS, 0);
+                const uint32_t child_base = uint32_t(ft.children.size());
+                ft.children.resize(ft.children.size() + (size_t(1) << bits), REF_LEAF);   // empty leaf: nothing matches
+                for (const auto& kv : parts) {
+                    const uint32_t h = (fold(kv.first, r1, r2) * mult) >> (32 - bits);
+                    const uint32_t ref = build(kv.second, used | common, depth + 1);
+                    ft.children[child_base + h] = ref;
+                }
+                uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
+                for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
+                n[NR_MULT] = mult;
+                n[NR_CFG] = (32 - bits) | (r1 << 5) | (r2 << 10);
+                n[NR_CHILD] = child_base;
+                return REF_NODE | node;
+            }
+            // No perfect hash found: fall through and scan (still correct).
+        }
+
+        // Single-bit split: candidates that do not check the bit go to both sides.
+        const size_t n_classes = class_count(vs);
+        if (n_classes > 2) {
+            size_t best_max = n_classes, best_sum = 0;
+            int best_bit = -1;
+            std::vector<uint32_t> best_zero, best_one;
+            for (int bit = 12; bit < 96; ++bit) {
+                const u128 m = ((u128)1) << bit;
+                if (used & m) continue;
+                std::vector<uint32_t> zero, one;
+                for (uint32_t v : vs) {
+                    const bool checks = (st[v].weakest() & m) != 0, set = (st[v].base96 & m) != 0;
+                    if (!checks || !set) zero.push_back(v);
+                    if (!checks || set) one.push_back(v);
+                }
+                if (zero.size() == vs.size() && one.size() == vs.size()) continue;
+                const size_t cz = class_count(zero), co = class_count(one);
+                const size_t mx = std::max(cz, co), sum = cz + co;
+                if (mx < best_max || (mx == best_max && best_bit >= 0 && sum < best_sum)) {
+                    best_max = mx; best_sum = sum; best_bit = bit; best_zero = zero; best_one = one;
+                }
+            }
+            if (best_bit >= 0 && best_max < n_classes) {
+                const uint32_t child_base = uint32_t(ft.children.size());
+                if (child_base + 2 >= (1u << 20)) throw std::runtime_error("match tree too large");
+                ft.children.resize(ft.children.size() + 2, REF_LEAF);
+                const u128 m = ((u128)1) << best_bit;
+                const uint32_t z = best_zero.empty() ? uint32_t(REF_LEAF) : build(best_zero, used | m, depth + 1);
+                const uint32_t o = best_one.empty() ? uint32_t(REF_LEAF) : build(best_one, used | m, depth + 1);
+                ft.children[child_base] = z;
+                ft.children[child_base + 1] = o;
+                return REF_BIT | child_base | (uint32_t(best_bit) << 20);
             }
         }
-        if (!ok) return make_leaf(vs);   // no perfect hash found: scan everything (still correct)
-
-        const uint32_t node = uint32_t(ft.nodes.size() / NR_WORDS);
-        ft.nodes.resize(ft.nodes.size() + NR_WORDS, 0);
-        const uint32_t child_base = uint32_t(ft.children.size());
-        ft.children.resize(ft.children.size() + (size_t(1) << bits), REF_LEAF);   // empty leaf: nothing matches
-        for (const auto& kv : parts) {
-            const uint32_t h = (fold(kv.first, r1, r2) * mult) >> (32 - bits);
-            const uint32_t ref = build(kv.second, used | common, depth + 1);
-            ft.children[child_base + h] = ref;
-        }
-        uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
-        for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
-        n[NR_MULT] = mult;
-        n[NR_CFG] = (32 - bits) | (r1 << 5) | (r2 << 10);
-        n[NR_CHILD] = child_base;
-        return REF_NODE | node;
+        return make_leaf(vs);
     }
 };
 
@@ -548,20 +612,23 @@ FlatTable FlatTable::compile(const IsaTable& t) {
                        (uint32_t(ik.ctrl_kind) << VF_CTRL_KIND_POS);
     }
 
-    // Dense ranks of the static tuples -> static rank keys.
-    std::map<std::tuple<int, int, int, int, int>, uint32_t> mid_rank;
-    std::map<std::tuple<int, int>, uint32_t> lo_rank;
-    for (const Static& s : st) { mid_rank[s.mid] = 0; lo_rank[s.lo] = 0; }
-    uint32_t r = 0;
-    for (auto& kv : mid_rank) kv.second = r++;
-    r = 0;
-    for (auto& kv : lo_rank) kv.second = r++;
-    if (mid_rank.size() >= (1u << 14) || lo_rank.size() >= (1u << 14))
-        throw std::runtime_error("too many distinct rank classes");
-    for (size_t vi = 0; vi < nv; ++vi) {
-        Static& s = st[vi];
-        s.key = (uint64_t(s.score < 0 ? 1 : 0) << 63) | (uint64_t(mid_rank[s.mid]) << 47) |
-                (uint64_t(lo_rank[s.lo]) << 25) | uint64_t(vi);
+    // Variants with the same field layout share one extraction record.
+    std::vector<uint32_t> ext_of(nv);
+    {
+        std::map<std::vector<uint32_t>, uint32_t> seen;
+        std::vector<uint32_t> unique;
+        for (size_t vi = 0; vi < nv; ++vi) {
+            std::vector<uint32_t> rec(ft.ext.begin() + vi * XR_WORDS, ft.ext.begin() + (vi + 1) * XR_WORDS);
+            auto it = seen.find(rec);
+            if (it == seen.end()) {
+                it = seen.emplace(rec, uint32_t(unique.size() / XR_WORDS)).first;
+                unique.insert(unique.end(), rec.begin(), rec.end());
+            }
+            ext_of[vi] = it->second;
+            ft.var[vi * VR_WORDS + VR_EXT] = it->second;
+        }
+        if (unique.size() / XR_WORDS > 0xFFFF) throw std::runtime_error("too many distinct field layouts");
+        ft.ext.swap(unique);
     }
 
     // Buckets on and_base bits 11:0, then the split tree inside each bucket.  Variants that
@@ -574,7 +641,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         if (st[vi].matchable()) buckets[b].push_back(uint32_t(vi));
     }
     std::vector<uint32_t> dir16(2048, 0), bucket_ref;
-    TreeBuilder tb{st, ft};
+    TreeBuilder tb{st, ext_of, ft};
     for (size_t b = 0; b < 4096; ++b) {
         if (!bucket_size[b]) continue;
         ++ft.n_buckets;

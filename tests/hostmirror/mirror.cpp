@@ -61,6 +61,13 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
+// The compiled table blob and its section offsets (BlobLayout as 14 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout14) {
+    Mirror* m = (Mirror*)h;
+    *blob = m->flat.blob.data();
+    static_assert(sizeof(BlobLayout) == 14 * sizeof(uint32_t), "layout size");
+    memcpy(layout14, &m->flat.at, sizeof(BlobLayout));
+}
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
     const Mirror* m = (const Mirror*)h;
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
