@@ -55,7 +55,7 @@ __device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t) {
     for (uint32_t i = threadIdx.x; i < quads; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
     __syncthreads();
     FlatView v = t;
-    v.hot = reinterpret_cast<const uint32_t*>(g_table_smem);
+    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem);
     return v;
 }
 
@@ -511,7 +511,7 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         const uint32_t* blob = nullptr;
         int rc = upload(c, d.get(), ft.blob, &blob);
         if (rc) return rc;
-        d->view.hot = blob; d->view.cold = blob; d->view.at = ft.at;
+        d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
         d->hot_bytes = ft.at.hot_words * 4;
         int optin = 0;
         CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));

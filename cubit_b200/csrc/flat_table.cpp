@@ -203,14 +203,13 @@ struct TreeBuilder {
             std::sort(mem.begin(), mem.end(), [&](uint32_t a, uint32_t b) { return key_of[a] < key_of[b]; });
             if (mem.size() > 255) throw std::runtime_error("class too large");
             const Static& best = st[mem[0]];
-            uint32_t rec[CR_WORDS] = {0}, extra[CX_WORDS] = {0};
+            uint32_t rec[CR_WORDS] = {0};
             for (int k = 0; k < 3; ++k) {
                 // A side that can never match gets mask 0 / base 1: (cc & 0) ^ 1 is never 0.
                 rec[CR_SMASK + k] = best.s_ok ? uint32_t(best.smask >> (32 * k)) : 0;
                 rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 1u : 0u);
-                extra[CX_BASE + k] = uint32_t(best.base96 >> (32 * k));
+                rec[CR_BASE + k] = uint32_t(best.base96 >> (32 * k));
             }
-            extra[CX_MEMBERS] = uint32_t(ft.members.size() / MR_WORDS);
             uint32_t info = uint32_t(mem.size()) << CI_MEMBERS_POS;
             // The broad test only adds something when it can succeed where the strict one fails.
             if (best.b_ok && !(best.s_ok && best.bmask == best.smask)) {
@@ -222,33 +221,30 @@ struct TreeBuilder {
                 info |= bi | CI_HAS_BROAD;
             }
             if (mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
-            // popcount(and_base & cc) on a strict match: the part under the mask is constant,
-            // the rest (typically baked guard bits) usually sits in one limb.
-            if (best.s_ok) {
-                info |= uint32_t(popcount128(best.base96 & best.smask)) << CI_POPC_POS;
-                const u128 dyn = best.base96 & ~best.smask;
-                int limbs = 0, which = 0;
-                for (int k = 0; k < 3; ++k)
-                    if (uint32_t(dyn >> (32 * k))) { ++limbs; which = k; }
-                if (limbs == 1) { info |= uint32_t(which + 1) << CI_DYN_POS; rec[CR_DYN_MASK] = uint32_t(dyn >> (32 * which)); }
-                else if (limbs > 1) info |= 4u << CI_DYN_POS;
-            } else {
-                info |= 4u << CI_DYN_POS;
-            }
             rec[CR_INFO] = info;
             rec[CR_FIRST_FLAGS] = best.flags;
             rec[CR_KEY] = key_of[mem[0]];
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
-            uint32_t any = 0;
-            for (uint32_t v : mem) {
-                any |= st[v].flags & 0xFFFFu;
-                ft.members.push_back(key_of[v]);
-                ft.members.push_back(st[v].flags);
-                ft.members.push_back(v | (ext_of[v] << 16));
+            uint32_t any = 0, tie_flags = 0;
+            for (uint32_t v : mem) any |= st[v].flags & 0xFFFFu;
+            if (mem.size() > 1) {
+                // Best member per choice flag (members are in rank order) and whether it is tied.
+                rec[CR_FLAGBEST] = uint32_t(ft.flagbest.size() / FB_WORDS);
+                uint32_t fb[FB_WORDS] = {0};
+                for (int f = 0; f < 16; ++f) {
+                    int seen = 0;
+                    uint32_t first_key = 0;
+                    for (uint32_t v : mem) {
+                        if (!((st[v].flags >> f) & 1u)) continue;
+                        if (seen == 0) { first_key = key_of[v]; fb[2 * f] = key_of[v]; fb[2 * f + 1] = v | (ext_of[v] << 16); }
+                        else if (seen == 1 && (key_of[v] >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT)) tie_flags |= 1u << f;
+                        ++seen;
+                    }
+                }
+                ft.flagbest.insert(ft.flagbest.end(), fb, fb + FB_WORDS);
             }
-            rec[CR_ANY_FLAGS] = any;
+            rec[CR_ANY_FLAGS] = any | (tie_flags << 16);
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
-            ft.class_extra.insert(ft.class_extra.end(), extra, extra + CX_WORDS);
         }
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
@@ -668,8 +664,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     L.ext = place(ft.ext);
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
-    L.class_extra = place(ft.class_extra);
-    L.members = place(ft.members);
+    L.flagbest = place(ft.flagbest);
     L.var = place(ft.var);
     L.gfields = place(ft.gfields);
     while (ft.blob.size() % 4) ft.blob.push_back(0);

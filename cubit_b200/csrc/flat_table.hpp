@@ -36,9 +36,8 @@ struct FlatTable {
     std::vector<uint32_t> nodes;     // NR_WORDS each
     std::vector<uint32_t> children;  // refs
     std::vector<uint32_t> classes;   // CR_WORDS each
-    std::vector<uint32_t> class_extra;  // CX_WORDS each
+    std::vector<uint32_t> flagbest;  // FB_WORDS per class that has several members
     std::vector<uint32_t> broad;     // BR_WORDS each
-    std::vector<uint32_t> members;   // MR_WORDS each
     std::vector<uint32_t> ext;       // XR_WORDS per variant
     std::vector<uint32_t> var;       // VR_WORDS per variant
     std::vector<uint32_t> gfields;

@@ -37,7 +37,7 @@ void* mir_load(const char* path) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_file(path);
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), 0, m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -46,7 +46,7 @@ void* mir_load_text(const char* text, uint64_t len) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_json_text(std::string(text, len));
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), 0, m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -61,12 +61,12 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 14 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout14) {
+// The compiled table blob and its section offsets (BlobLayout as 13 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout13) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 14 * sizeof(uint32_t), "layout size");
-    memcpy(layout14, &m->flat.at, sizeof(BlobLayout));
+    static_assert(sizeof(BlobLayout) == 13 * sizeof(uint32_t), "layout size");
+    memcpy(layout13, &m->flat.at, sizeof(BlobLayout));
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
     const Mirror* m = (const Mirror*)h;
