@@ -158,7 +158,9 @@ enum { GC_UNIFORM = 0, GC_UREG = 1, GC_MOD8 = 2, GC_REG = 3, GF_NOT_STORED = 0x1
 struct BlobLayout {
     uint32_t dir16;       // 4096 u16 (two per u32): bucket number + 1, 0 = no variant has these opcode bits
     uint32_t bucket_ref;  // one ref per bucket
-    uint32_t nodes, children, classes, broad, ext;
+    // Records wider than 16 bytes are stored quad by quad (all first quads, then all second
+    // quads, ...): a 16-byte stride spreads records over eight bank groups of shared memory.
+    uint32_t nodes[2], children, classes[4], broad[2], ext[2];
     uint32_t hot_words;   // everything above lies below this offset
     uint32_t flagbest, var, gfields;
     uint32_t total_words;
@@ -289,8 +291,8 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
             const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
             child = ref_index(ref) + ((limb >> (bit & 31u)) & 1u);
         } else {
-            const uint32_t n = t.at.nodes + ref_index(ref) * NR_WORDS;
-            const Quad a = HOT::q(t, n), b = HOT::q(t, n + 4);
+            const uint32_t n = ref_index(ref) * 4u;
+            const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
             const uint32_t cfg = b.x;
             const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, (cfg >> 5) & 31u) ^ cb_rotl(c2 & a.z, (cfg >> 10) & 31u);
             child = b.y + ((f * a.w) >> (cfg & 31u));
@@ -302,14 +304,14 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
     return ST_OK;
 }
 
-// Tests a class against cc: 0 strict match, 2 broad match, 3 no match.
+// Tests class `ci` against cc: 0 strict match, 2 broad match, 3 no match.
 template <class HOT>
-CB_HD uint32_t class_match(const FlatView& t, uint32_t r, uint32_t c0, uint32_t c1, uint32_t c2) {
-    const Quad a = HOT::q(t, r), b = HOT::q(t, r + 4);
+CB_HD uint32_t class_match(const FlatView& t, uint32_t ci, uint32_t c0, uint32_t c1, uint32_t c2) {
+    const Quad a = HOT::q(t, t.at.classes[0] + ci * 4u), b = HOT::q(t, t.at.classes[1] + ci * 4u);
     if ((((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0) return 0;
     if (b.z & CI_HAS_BROAD) {
-        const uint32_t br = t.at.broad + (b.z & CI_BROAD_MASK) * BR_WORDS;
-        const Quad m = HOT::q(t, br), v = HOT::q(t, br + 4);
+        const uint32_t br = (b.z & CI_BROAD_MASK) * 4u;
+        const Quad m = HOT::q(t, t.at.broad[0] + br), v = HOT::q(t, t.at.broad[1] + br);
         if ((((c0 & m.x) ^ m.w) | ((c1 & m.y) ^ v.x) | ((c2 & m.z) ^ v.y)) == 0) return 2;
     }
     return 3;
@@ -379,11 +381,11 @@ CB_HD uint32_t choose_rule(uint32_t any, uint32_t first_fl, uint32_t c0, uint32_
 
 // Folds the best member of one matching class that carries `need` into the running best.
 template <class HOT>
-CB_HD void fold_flagged(const FlatView& t, uint32_t r, uint32_t prio, uint32_t need,
+CB_HD void fold_flagged(const FlatView& t, uint32_t ci, uint32_t prio, uint32_t need,
                         uint32_t c0, uint32_t c1, uint32_t c2, uint32_t* win_key, uint32_t* win_best, uint32_t* tie) {
-    const Quad q2 = HOT::q(t, r + 8);
+    const Quad q2 = HOT::q(t, t.at.classes[2] + ci * 4u);
     if (!(q2.y & need)) return;
-    const Quad q1 = HOT::q(t, r + 4), q3 = HOT::q(t, r + 12);
+    const Quad q1 = HOT::q(t, t.at.classes[1] + ci * 4u), q3 = HOT::q(t, t.at.classes[3] + ci * 4u);
     uint32_t key = q2.x, best = q2.z, within = 0;
     if (((q1.z >> CI_MEMBERS_POS) & 0xFFu) > 1u) {
         const uint32_t f = cb_lowest_bit(need);
@@ -420,13 +422,12 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     uint32_t strict0 = 0, broad0 = 0;
     for (uint32_t base = 0; base < count; base += 32) {
         const uint32_t chunk = (count - base) < 32u ? (count - base) : 32u;
-        const uint32_t r0 = t.at.classes + (start + base) * CR_WORDS;
+        const uint32_t r0 = start + base;
         uint32_t strict = 0, broad = 0;
         {
-            uint32_t r = r0;
             uint32_t bit = 1u;
-            for (uint32_t i = 0; i < chunk; ++i, r += CR_WORDS, bit <<= 1) {
-                const uint32_t prio = class_match<HOT>(t, r, c0, c1, c2);
+            for (uint32_t i = 0; i < chunk; ++i, bit <<= 1) {
+                const uint32_t prio = class_match<HOT>(t, r0 + i, c0, c1, c2);
                 strict |= prio == 0 ? bit : 0u;
                 broad |= prio == 2 ? bit : 0u;
             }
@@ -434,8 +435,8 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         if (base == 0) { strict0 = strict; broad0 = broad; }
         for (uint32_t mm = strict | broad; mm; mm &= mm - 1u) {
             const uint32_t i = cb_lowest_bit(mm);
-            const uint32_t r = r0 + i * CR_WORDS;
-            const Quad q1 = HOT::q(t, r + 4), q2 = HOT::q(t, r + 8), q3 = HOT::q(t, r + 12);
+            const uint32_t r = (r0 + i) * 4u;
+            const Quad q1 = HOT::q(t, t.at.classes[1] + r), q2 = HOT::q(t, t.at.classes[2] + r), q3 = HOT::q(t, t.at.classes[3] + r);
             const uint32_t k = q2.x | dynamic_key(q3, ((broad >> i) & 1u) << 1, c0, c1, c2);
             any |= q2.y;
             const bool same = (k >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT), better = k < first_key;
@@ -453,16 +454,15 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     if (need && !(first_fl & need)) {
         // Second pass (uncommon): best member carrying `need` among the matching classes.
         uint32_t win_key = 0xFFFFFFFFu, win_best = FORM_NONE, tie2 = 0;
-        const uint32_t r0 = t.at.classes + start * CR_WORDS;
         if (count <= 32) {
             for (uint32_t mm = strict0 | broad0; mm; mm &= mm - 1u) {
                 const uint32_t i = cb_lowest_bit(mm);
-                fold_flagged<HOT>(t, r0 + i * CR_WORDS, ((broad0 >> i) & 1u) << 1, need, c0, c1, c2, &win_key, &win_best, &tie2);
+                fold_flagged<HOT>(t, start + i, ((broad0 >> i) & 1u) << 1, need, c0, c1, c2, &win_key, &win_best, &tie2);
             }
         } else {
             for (uint32_t i = 0; i < count; ++i) {
-                const uint32_t prio = class_match<HOT>(t, r0 + i * CR_WORDS, c0, c1, c2);
-                if (prio != 3) fold_flagged<HOT>(t, r0 + i * CR_WORDS, prio, need, c0, c1, c2, &win_key, &win_best, &tie2);
+                const uint32_t prio = class_match<HOT>(t, start + i, c0, c1, c2);
+                if (prio != 3) fold_flagged<HOT>(t, start + i, prio, need, c0, c1, c2, &win_key, &win_best, &tie2);
             }
         }
         if (win_key != 0xFFFFFFFFu) { *best = win_best; *tie = tie_first | tie2; }
@@ -479,8 +479,7 @@ CB_HD uint32_t ctrl_from_raw(uint32_t w0, uint32_t w3) {
 // Field values of `variant` out of cc into the 8 slots; returns the variant's synth_ok bits.
 template <class HOT>
 CB_HD uint32_t extract_slots(const FlatView& t, uint32_t ext_index, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t slots[8]) {
-    const uint32_t x = t.at.ext + ext_index * XR_WORDS;
-    const Quad dq = HOT::q(t, x), mq = HOT::q(t, x + 4);
+    const Quad dq = HOT::q(t, t.at.ext[0] + ext_index * 4u), mq = HOT::q(t, t.at.ext[1] + ext_index * 4u);
     const uint32_t desc[4] = {dq.x, dq.y, dq.z, dq.w};
     const uint32_t cfg = mq.w;
     const uint32_t m0 = mq.x, m1 = mq.y, m2 = mq.z;
@@ -534,8 +533,8 @@ CB_HD void encode_record(const FlatView& t, uint32_t form, const uint32_t slots[
                          uint32_t* w0, uint32_t* w1, uint32_t* w2, uint32_t* w3) {
     if (form >= t.at.n_variants) { *w0 = *w1 = *w2 = *w3 = 0; return; }
     const uint32_t* v = t.cold + t.at.var + form * VR_WORDS;
-    const uint32_t x = t.at.ext + (cb_ld(v + VR_EXT) & 0xFFFFu) * XR_WORDS;
-    const Quad dq = HOT::q(t, x), mq = HOT::q(t, x + 4);
+    const uint32_t x = (cb_ld(v + VR_EXT) & 0xFFFFu) * 4u;
+    const Quad dq = HOT::q(t, t.at.ext[0] + x), mq = HOT::q(t, t.at.ext[1] + x);
     const uint32_t desc[4] = {dq.x, dq.y, dq.z, dq.w};
     uint32_t code[3] = {cb_ld(v + VR_BASE), cb_ld(v + VR_BASE + 1), cb_ld(v + VR_BASE + 2)};
     const uint32_t cfg = mq.w;

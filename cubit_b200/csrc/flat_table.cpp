@@ -657,11 +657,17 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     BlobLayout& L = ft.at;
     L.dir16 = place(dir16);
     L.bucket_ref = place(bucket_ref);
-    L.nodes = place(ft.nodes);
+    // Quad `q` of every record of a section whose records are `words` wide.
+    auto quad_plane = [](const std::vector<uint32_t>& src, size_t words, size_t q) {
+        std::vector<uint32_t> out;
+        for (size_t r = 0; r * words < src.size(); ++r) out.insert(out.end(), src.begin() + r * words + 4 * q, src.begin() + r * words + 4 * q + 4);
+        return out;
+    };
+    for (size_t q = 0; q < 2; ++q) L.nodes[q] = place(quad_plane(ft.nodes, NR_WORDS, q));
     L.children = place(ft.children);
-    L.classes = place(ft.classes);
-    L.broad = place(ft.broad);
-    L.ext = place(ft.ext);
+    for (size_t q = 0; q < 4; ++q) L.classes[q] = place(quad_plane(ft.classes, CR_WORDS, q));
+    for (size_t q = 0; q < 2; ++q) L.broad[q] = place(quad_plane(ft.broad, BR_WORDS, q));
+    for (size_t q = 0; q < 2; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
     L.flagbest = place(ft.flagbest);

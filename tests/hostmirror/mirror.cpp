@@ -61,12 +61,46 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 13 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout13) {
+// The compiled table blob and its section offsets (BlobLayout as 19 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout19) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 13 * sizeof(uint32_t), "layout size");
-    memcpy(layout13, &m->flat.at, sizeof(BlobLayout));
+    static_assert(sizeof(BlobLayout) == 19 * sizeof(uint32_t), "layout size");
+    memcpy(layout19, &m->flat.at, sizeof(BlobLayout));
+}
+// Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
+void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_classes, uint8_t* n_match, uint8_t* depth) {
+    const Mirror* m = (const Mirror*)h;
+    const FlatView& t = m->view;
+    for (uint64_t i = 0; i < n; ++i) {
+        const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
+        uint32_t start = 0, count = 0, steps = 0;
+        const uint32_t op = c0 & 0xFFFu;
+        const uint32_t bucket = (t.hot[t.at.dir16 + (op >> 1)] >> (16 * (op & 1))) & 0xFFFFu;
+        if (bucket) {
+            uint32_t ref = t.hot[t.at.bucket_ref + bucket - 1];
+            while (!(ref & REF_LEAF)) {
+                ++steps;
+                uint32_t child;
+                if (ref & REF_BIT) {
+                    const uint32_t bit = (ref >> 20) & 127u, w = bit >> 5;
+                    const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
+                    child = ref_index(ref) + ((limb >> (bit & 31u)) & 1u);
+                } else {
+                    const uint32_t* na = t.hot + t.at.nodes[0] + ref_index(ref) * 4;
+                    const uint32_t* nb = t.hot + t.at.nodes[1] + ref_index(ref) * 4;
+                    const uint32_t f = (c0 & na[0]) ^ cb_rotl(c1 & na[1], (nb[0] >> 5) & 31u) ^ cb_rotl(c2 & na[2], (nb[0] >> 10) & 31u);
+                    child = nb[1] + ((f * na[3]) >> (nb[0] & 31u));
+                }
+                ref = t.hot[t.at.children + child];
+            }
+            start = ref_index(ref); count = ref_count(ref);
+        }
+        uint32_t matches = 0;
+        for (uint32_t k = 0; k < count; ++k)
+            matches += class_match<HotPlain>(t, start + k, c0, c1, c2) != 3;
+        n_classes[i] = (uint8_t)count; n_match[i] = (uint8_t)matches; depth[i] = (uint8_t)steps;
+    }
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
     const Mirror* m = (const Mirror*)h;
