@@ -41,6 +41,8 @@ SIGNATURES = {
     "cubit_host_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cubit_decode_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.POINTER(Counts), C.c_int, C.c_void_p]),
+    "cubit_decode_batch_static": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.POINTER(Counts)]),
     "cubit_encode_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_int,
                                      C.c_void_p]),
     "cubit_roundtrip_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.POINTER(Counts), C.c_int,

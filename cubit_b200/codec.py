@@ -24,6 +24,7 @@ FORM_NONE = 0xFFFF
 RT_EXACT, RT_MISMATCH, RT_REJECTED = 0, 1, 2
 SCHED_MASK = 0x1FFFF << 105
 NOT_STORED = 0xFFFFFFFF
+STATIC_MAX_WORDS = 65536
 
 
 class CubitError(RuntimeError):
@@ -154,6 +155,19 @@ class Codec:
         counts = Counts()
         self._check(self._lib.cubit_decode_batch(self._ctx, _ptr(w), n, _ptr(form), _ptr(slots), _ptr(ctrl),
                                                  C.byref(counts), MEM_HOST, None))
+        return form, slots, ctrl, counts.as_dict()
+
+    def decode_batch_static(self, words, device_slot: int = 0):
+        """decode_batch for at most STATIC_MAX_WORDS words without any device allocation: the batch is
+        staged through a fixed array built into the library.  For callers that must not call cudaMalloc
+        while running (device memory reserved by someone else, or no tolerance for its implicit
+        synchronisation).  Calls on one device must not overlap."""
+        w = self._words(words)
+        n = len(w)
+        form = np.empty(n, np.uint16); slots = np.empty((8, n), np.uint32); ctrl = np.empty(n, np.uint32)
+        counts = Counts()
+        self._check(self._lib.cubit_decode_batch_static(self._ctx, device_slot, _ptr(w), n, _ptr(form), _ptr(slots),
+                                                        _ptr(ctrl), C.byref(counts)))
         return form, slots, ctrl, counts.as_dict()
 
     def encode_batch(self, form, slots, ctrl) -> np.ndarray:

@@ -154,6 +154,21 @@ synth_kernel(FlatView t, SynthView g, uint64_t first, uint64_t n, uint4* __restr
     }
 }
 
+// ---- scratch of the allocation-free entry point ----------------------------------------------
+//
+// cubit_decode_batch_static stages one batch through this array instead of memory from
+// cudaMalloc: the words, the three record planes the kernel writes, and the launch counters.
+// It is part of the library image, so every GPU that loads the library carries it
+// (about 3.4 MiB) until the process exits.  In host code the name below is only a handle for
+// cudaGetSymbolAddress; the kernel is given the device address obtained from it.
+constexpr uint64_t kStaticMaxWords = CUBIT_STATIC_MAX_WORDS;
+constexpr uint64_t kStaticFormOff = kStaticMaxWords * 16;
+constexpr uint64_t kStaticSlotsOff = kStaticFormOff + kStaticMaxWords * 2;
+constexpr uint64_t kStaticCtrlOff = kStaticSlotsOff + kStaticMaxWords * 32;
+constexpr uint64_t kStaticCountersOff = kStaticCtrlOff + kStaticMaxWords * 4;
+constexpr uint64_t kStaticBytes = kStaticCountersOff + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
 // ---- context -----------------------------------------------------------------------------
 
 thread_local std::string g_create_error;
@@ -173,6 +188,8 @@ struct DeviceState {
     uint64_t stage_bytes = 0;
     cudaStream_t stream = nullptr;
     std::mutex stage_mu;
+    // Device address of g_static_scratch on this device, looked up on first use.
+    unsigned char* static_scratch = nullptr;
     // Stream generator tables, one per (mix, seed).
     std::map<std::pair<uint32_t, uint64_t>, SynthView> synth;
 };
@@ -733,6 +750,48 @@ extern "C" int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, ui
         if (ctrl) CU_TRY(ctx, cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
         CU_TRY(ctx, cudaStreamSynchronize(d->stream));
     }
+    return CUBIT_OK;
+}
+
+// Host-buffer decode of a small batch that allocates nothing: see include/cubit_b200.h.
+extern "C" int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const void* words, uint64_t n, uint16_t* form,
+                                         uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (counts) memset(counts, 0, sizeof *counts);
+    if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "decode needs a CUDA device; this context has none");
+    if (device_slot < 0 || (size_t)device_slot >= ctx->devs.size()) return fail(ctx, CUBIT_ERR_INVALID, "device_slot out of range");
+    if (n > kStaticMaxWords)
+        return fail(ctx, CUBIT_ERR_INVALID, "batch exceeds CUBIT_STATIC_MAX_WORDS (65536 words), the capacity of the built-in "
+                                            "scratch; split it or use cubit_decode_batch");
+    if (n == 0) return CUBIT_OK;
+    if (!words || !form || !slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
+    DeviceState* d = ctx->devs[(size_t)device_slot].get();
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    {
+        // One-time set-up per device, with that device current: the symbol's address there.
+        std::lock_guard<std::mutex> g(d->mu);
+        if (!d->static_scratch) {
+            unsigned char* p = nullptr;
+            CU_TRY(ctx, cudaGetSymbolAddress((void**)&p, g_static_scratch));
+            d->static_scratch = p;
+        }
+    }
+    unsigned char* st = d->static_scratch;
+    unsigned long long* dc = (unsigned long long*)(st + kStaticCountersOff);
+    unsigned long long host_counts[CNT_WORDS] = {0, 0, 0, 0, 0};
+    // The array keeps what the previous call left: the counters are accumulated into, so they
+    // are cleared; the record planes are fully overwritten for the first n entries.
+    CU_TRY(ctx, cudaMemsetAsync(dc, 0, sizeof host_counts, d->stream));
+    CU_TRY(ctx, cudaMemcpyAsync(st, words, n * 16, cudaMemcpyHostToDevice, d->stream));
+    launch_decode(d, d->stream, (const uint4*)st, n, (uint16_t*)(st + kStaticFormOff), (uint32_t*)(st + kStaticSlotsOff), n,
+                  (uint32_t*)(st + kStaticCtrlOff), dc);
+    CU_TRY(ctx, cudaGetLastError());
+    CU_TRY(ctx, cudaMemcpyAsync(form, st + kStaticFormOff, n * 2, cudaMemcpyDeviceToHost, d->stream));
+    CU_TRY(ctx, cudaMemcpyAsync(slots, st + kStaticSlotsOff, n * 32, cudaMemcpyDeviceToHost, d->stream));
+    CU_TRY(ctx, cudaMemcpyAsync(ctrl, st + kStaticCtrlOff, n * 4, cudaMemcpyDeviceToHost, d->stream));
+    CU_TRY(ctx, cudaMemcpyAsync(host_counts, dc, sizeof host_counts, cudaMemcpyDeviceToHost, d->stream));
+    CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    if (counts) add_counts(counts, host_counts);
     return CUBIT_OK;
 }
 

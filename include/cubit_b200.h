@@ -143,6 +143,30 @@ int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, uint32_t nois
                       uint64_t n, void* words, uint16_t* form, uint32_t* slots, uint32_t* ctrl,
                       int mem_kind, void* stream);
 
+/* Largest batch cubit_decode_batch_static accepts. */
+#define CUBIT_STATIC_MAX_WORDS 65536
+
+/* Host-buffer decode that allocates nothing (no counterpart in the reference, which has no
+ * device memory to manage).  It is for callers that must not allocate device memory once they
+ * are running: a process in which another component has already reserved the GPU's memory, so
+ * that cudaMalloc would fail, or a latency-critical thread that cannot afford the implicit
+ * device synchronisation of cudaMalloc / cudaFree.  cubit_decode_batch grows a staging buffer
+ * with cudaMalloc when it is handed host memory; this entry point stages through a fixed
+ * array built into the library instead (about 3.4 MiB per GPU, held until the process exits),
+ * and calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - words / form / slots / ctrl are host buffers as for cubit_decode_batch(CUBIT_MEM_HOST),
+ *     slots being u32[8][n]; results are identical to cubit_decode_batch's.
+ *   - n above CUBIT_STATIC_MAX_WORDS is refused with CUBIT_ERR_INVALID.
+ *   - device_slot picks one of the context's devices by position in the list given to
+ *     cubit_ctx_create.  The first call on a device looks up the array's address there
+ *     (a one-time set-up); make that first call before starting any stream capture.
+ *   - All calls on one device share the array.  It keeps the previous call's contents; the
+ *     entry point clears the counters it accumulates into and overwrites the rest.  Two calls
+ *     that overlap in time on the same device race on it: the caller must serialise them.
+ * The call returns when the results are in the host buffers. */
+int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const void* words, uint64_t n, uint16_t* form,
+                              uint32_t* slots, uint32_t* ctrl, cubit_counts* counts);
+
 /* ---- cubin (ELF) ------------------------------------------------------------------------ */
 
 /* Replaces CubinFile::from_bytes (reference src/elf.rs:29-58): lists PROGBITS sections named
