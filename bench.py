@@ -29,9 +29,20 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "decode_throughput"
 UNIT = "Ginsn/s"
-DECODE_BYTES_PER_INSN = 54          # 16 in + 2 (form) + 32 (8 slots) + 4 (ctrl) out
+# Algorithmic bytes per instruction: decode 16 in + 2 (form) + 32 (8 slots) + 4 (ctrl) out; encode the reverse;
+# roundtrip 16 in + 1 status byte out.
+WORKLOADS = {
+    "decode": {"metric": "decode_throughput", "bytes": 54, "kernel": "decode_kernel", "noise_ppm": 0,
+               "text": "cfg1 batch decode: 64 Mi SM120 words per GPU, forms Zipf(1.1) over a seeded permutation of the "
+                       "keys, SoA records out"},
+    "encode": {"metric": "encode_throughput", "bytes": 54, "kernel": "encode_kernel", "noise_ppm": 0,
+               "text": "cfg2 batch encode: the generator's 64 Mi (form, 8 slots, ctrl) records per GPU to words"},
+    "roundtrip": {"metric": "roundtrip_throughput", "bytes": 17, "kernel": "roundtrip_kernel", "noise_ppm": 10000,
+                  "text": "cfg3 fused roundtrip (decode, encode, compare): 64 Mi words per GPU, Zipf(1.1) forms, 1 % raw "
+                          "random words, one status byte out"},
+}
+METRIC = WORKLOADS["decode"]["metric"]
 DEFAULT_WORDS = 64 * 1024 * 1024    # 1 GiB of 16-byte words
 STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
@@ -204,6 +215,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--words", type=int, default=DEFAULT_WORDS, help="words per GPU per step")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS),
+                    help="decode is the headline (cfg1); encode / roundtrip report the other two kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     args = ap.parse_args()
@@ -230,17 +243,27 @@ def main():
     n = args.words
     first = rank * n    # every rank owns its own contiguous range of one stream
 
+    wl = WORKLOADS[args.workload]
     words = torch.empty(n * 16, dtype=torch.uint8, device=dev)
     form = torch.empty(n, dtype=torch.int16, device=dev)
     slots = torch.empty(8 * n, dtype=torch.int32, device=dev)
     ctrl = torch.empty(n, dtype=torch.int32, device=dev)
+    status = torch.empty(n, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
     sptr = stream.cuda_stream
-    codec.synth_device(cubit_b200.MIX_ZIPF, STREAM_SEED, n, words_ptr=words.data_ptr(), first=first, stream=sptr)
+    codec.synth_device(cubit_b200.MIX_ZIPF, STREAM_SEED, n, words_ptr=words.data_ptr(), form_ptr=form.data_ptr(),
+                       slots_ptr=slots.data_ptr(), ctrl_ptr=ctrl.data_ptr(), noise_ppm=wl["noise_ppm"], first=first, stream=sptr)
     torch.cuda.synchronize()
 
-    def step():
-        codec.decode_device(words.data_ptr(), n, form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(), stream=sptr)
+    if args.workload == "decode":
+        def step():
+            codec.decode_device(words.data_ptr(), n, form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(), stream=sptr)
+    elif args.workload == "encode":
+        def step():
+            codec.encode_device(form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(), n, words.data_ptr(), stream=sptr)
+    else:
+        def step():
+            codec.roundtrip_device(words.data_ptr(), n, status.data_ptr(), stream=sptr)
 
     def barrier():
         if world > 1:
@@ -266,30 +289,35 @@ def main():
     total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     value = world * n / (ms_per_step * 1e-3) / 1e9
-    counts = codec.decode_device(words.data_ptr(), n, form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(), stream=sptr,
-                                 want_counts=True)
+    if args.workload == "roundtrip":
+        counts = codec.roundtrip_device(words.data_ptr(), n, status.data_ptr(), stream=sptr, want_counts=True)
+    elif args.workload == "decode":
+        counts = codec.decode_device(words.data_ptr(), n, form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(), stream=sptr,
+                                     want_counts=True)
+    else:
+        counts = None
 
     e2e, cpu = None, None
-    if not args.no_e2e:
+    if not args.no_e2e and args.workload == "decode":
         e2e, cpu = run_e2e(args, codec, n, first, form, barrier, rank, world, dev)
 
     if rank == 0:
         peak, peak_kind = hbm_peak()
         kernel_ms = statistics.mean(per_launch_ms)
-        achieved = DECODE_BYTES_PER_INSN * n / (kernel_ms * 1e-3) / 1e9
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        achieved = wl["bytes"] * n / (kernel_ms * 1e-3) / 1e9
+        line = {"metric": wl["metric"], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-                "config": {"workload": "cfg1 batch decode: 64 Mi SM120 words per GPU, forms Zipf(1.1) over a seeded "
-                                       "permutation of the keys, SoA records out",
-                           "words_per_gpu": n, "seed": STREAM_SEED, "l2": "inputs larger than L2 (1 GiB in, 2.4 GiB out)",
+                "config": {"workload": wl["text"],
+                           "words_per_gpu": n, "seed": STREAM_SEED, "l2": "inputs larger than L2 (1 GiB of words per GPU)",
                            "sharding": "contiguous ranges of one stream, no collective"},
                 "e2e": e2e,
                 "gpu_launches": args.steps,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "peak_kind": f"of {peak_kind}", "kernel": "decode_kernel", "kernel_ms": kernel_ms,
-                             "bytes_per_insn": DECODE_BYTES_PER_INSN,
-                             "traffic": None if NCU_DRAM_BYTES_PER_WORD is None else NCU_DRAM_BYTES_PER_WORD * n},
+                             "peak_kind": f"of {peak_kind}", "kernel": wl["kernel"], "kernel_ms": kernel_ms,
+                             "bytes_per_insn": wl["bytes"],
+                             "traffic": None if (NCU_DRAM_BYTES_PER_WORD is None or args.workload != "decode")
+                             else NCU_DRAM_BYTES_PER_WORD * n},
                 "counts": counts, "clocks": clocks}
         if cpu:
             line["cpu_baseline"] = cpu

@@ -198,10 +198,39 @@ struct TreeBuilder {
         }
         const uint32_t first_class = uint32_t(ft.classes.size() / CR_WORDS);
         if (order.size() > 255 || first_class + order.size() >= (1u << 20)) throw std::runtime_error("leaf too large");
-        for (const ClassKey& ck : order) {
+        // Members in rank order inside a class; classes in rank order of their best member.
+        for (auto& kv : groups)
+            std::sort(kv.second.begin(), kv.second.end(), [&](uint32_t a, uint32_t b) { return key_of[a] < key_of[b]; });
+        // Static rank order of classes.  Two strictly matching classes compare by
+        // (score sign, middle rank, popcount(and_base & word), low rank, canonical position).  The
+        // popcount splits into a constant part under the strict mask and a word-dependent part
+        // over and_base bits outside it (mostly baked guard bits); classes with the *same* outside
+        // bits get the same word-dependent part, so their order is static.
+        auto sort_key = [&](const ClassKey& c) {
+            const uint32_t v = groups[c][0], k = key_of[v];
+            const Static& b = st[v];
+            const int pst = b.s_ok ? popcount128(b.base96 & b.smask) : 0;
+            return std::make_tuple(k >> 22, -pst, k & 0x7FFFu);
+        };
+        std::sort(order.begin(), order.end(), [&](const ClassKey& a, const ClassKey& b) { return sort_key(a) < sort_key(b); });
+        // CR_GROUP: classes whose order against this one is NOT settled by position — same
+        // (score sign, middle rank) and either different outside bits (word-dependent) or an
+        // identical static tuple (a tie the ranking loop has to report).
+        auto outside = [&](const ClassKey& c) { const Static& b = st[groups[c][0]]; return b.s_ok ? (b.base96 & ~b.smask) : ~(u128)0; };
+        auto unsettled = [&](const ClassKey& a, const ClassKey& b) {
+            const auto ka = sort_key(a), kb = sort_key(b);
+            if (std::get<0>(ka) != std::get<0>(kb)) return false;
+            if (!st[groups[a][0]].s_ok || !st[groups[b][0]].s_ok) return true;
+            if (outside(a) != outside(b)) return true;
+            return std::get<1>(ka) == std::get<1>(kb) && (std::get<2>(ka) >> 8) == (std::get<2>(kb) >> 8);
+        };
+        for (size_t ci = 0; ci < order.size(); ++ci) {
+            const ClassKey& ck = order[ci];
             std::vector<uint32_t>& mem = groups[ck];
-            std::sort(mem.begin(), mem.end(), [&](uint32_t a, uint32_t b) { return key_of[a] < key_of[b]; });
             if (mem.size() > 255) throw std::runtime_error("class too large");
+            uint32_t group_mask = 0;
+            for (size_t cj = 0; cj < order.size() && cj < 32; ++cj)
+                if (cj == ci || unsettled(order[cj], ck)) group_mask |= 1u << cj;
             const Static& best = st[mem[0]];
             uint32_t rec[CR_WORDS] = {0};
             for (int k = 0; k < 3; ++k) {
@@ -222,6 +251,7 @@ struct TreeBuilder {
             }
             if (mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
             rec[CR_INFO] = info;
+            rec[CR_GROUP] = group_mask;
             rec[CR_FIRST_FLAGS] = best.flags;
             rec[CR_KEY] = key_of[mem[0]];
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);

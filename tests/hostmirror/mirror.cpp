@@ -98,8 +98,57 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
         }
         uint32_t matches = 0;
         for (uint32_t k = 0; k < count; ++k)
-            matches += class_match<HotPlain>(t, start + k, c0, c1, c2) != 3;
+            { uint32_t fl; matches += class_match<HotPlain>(t, start + k, c0, c1, c2, &fl) != 3; }
         n_classes[i] = (uint8_t)count; n_match[i] = (uint8_t)matches; depth[i] = (uint8_t)steps;
+    }
+}
+// Per word: the choice flag the rules ask for (0 none) and whether the top candidate already has it.
+void mir_rule_stats(void* h, const uint32_t* words, uint64_t n, uint32_t* need_out, uint8_t* first_has) {
+    const Mirror* m = (const Mirror*)h;
+    const FlatView& t = m->view;
+    for (uint64_t i = 0; i < n; ++i) {
+        const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
+        need_out[i] = 0; first_has[i] = 0;
+        uint32_t start, count;
+        if (find_leaf<HotPlain>(t, c0, c1, c2, &start, &count) != ST_OK) continue;
+        uint32_t first_key = 0xFFFFFFFFu, first_fl = 0, any = 0;
+        for (uint32_t k = 0; k < count; ++k) {
+            uint32_t fl;
+            const uint32_t prio = class_match<HotPlain>(t, start + k, c0, c1, c2, &fl);
+            if (prio == 3) continue;
+            const uint32_t r = (start + k) * 4;
+            const Quad q2 = HotPlain::q(t, t.at.classes[2] + r), q3 = HotPlain::q(t, t.at.classes[3] + r);
+            const uint32_t key = q2.x | dynamic_key(q3, prio, c0, c1, c2);
+            any |= fl;
+            if (key < first_key) { first_key = key; first_fl = q2.y; }
+        }
+        if (first_key == 0xFFFFFFFFu) continue;
+        const uint32_t need = choose_rule(any & 0xFFFF, first_fl, c0, c1, c2);
+        need_out[i] = need; first_has[i] = (first_fl & need) != 0;
+    }
+}
+// Per word: how many classes the ranking loop has to compare (0: decided by static order alone).
+void mir_rank_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* loop_len) {
+    const Mirror* m = (const Mirror*)h;
+    const FlatView& t = m->view;
+    for (uint64_t i = 0; i < n; ++i) {
+        const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
+        loop_len[i] = 0;
+        uint32_t start, count;
+        if (find_leaf<HotPlain>(t, c0, c1, c2, &start, &count) != ST_OK || count > 32) continue;
+        uint32_t strict = 0, broad = 0;
+        for (uint32_t k = 0; k < count; ++k) {
+            uint32_t fl;
+            const uint32_t prio = class_match<HotPlain>(t, start + k, c0, c1, c2, &fl);
+            strict |= (prio == 0) << k; broad |= (prio == 2) << k;
+        }
+        uint32_t mm = strict | broad;
+        if (broad == 0 && strict) {
+            const uint32_t f = cb_lowest_bit(strict);
+            mm = HotPlain::q(t, t.at.classes[3] + (start + f) * 4u).w & strict;
+            if (mm == (1u << f)) mm = 0;
+        }
+        loop_len[i] = (uint8_t)__builtin_popcount(mm);
     }
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {
