@@ -42,20 +42,20 @@ enum { CNT_DECODED = 0, CNT_REJECTED, CNT_TIE, CNT_EXACT, CNT_MISMATCH, CNT_WORD
 
 extern __shared__ uint4 g_table_smem[];
 
-// Gives the view the kernel works with: for HotShared the hot part of the blob is first
-// copied into dynamic shared memory by the whole CTA.
+// Gives the view the kernel works with: for HotShared the words [begin, end) of the blob are
+// first copied into dynamic shared memory by the whole CTA.
 template <class HOT>
-__device__ __forceinline__ FlatView stage_table(const FlatView& t) {
+__device__ __forceinline__ FlatView stage_table(const FlatView& t, uint32_t, uint32_t) {
     return t;
 }
 template <>
-__device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t) {
-    const uint4* src = reinterpret_cast<const uint4*>(t.cold);
-    const uint32_t quads = t.at.hot_words / 4;
+__device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t, uint32_t begin, uint32_t end) {
+    const uint4* src = reinterpret_cast<const uint4*>(t.cold + begin);
+    const uint32_t quads = (end - begin) / 4;
     for (uint32_t i = threadIdx.x; i < quads; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
     __syncthreads();
     FlatView v = t;
-    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem);
+    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem) - begin * 4u;
     return v;
 }
 
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockSh
 decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
-    const FlatView t = stage_table<HOT>(tg);
+    const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
     uint32_t tally[3] = {0, 0, 0};
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
@@ -106,14 +106,15 @@ template <class HOT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
 encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
               uint64_t slot_stride, const uint32_t* __restrict__ ctrl, uint64_t n, uint4* __restrict__ words) {
-    const FlatView t = stage_table<HOT>(tg);
+    // The encode kernel stages its own window: extraction and variant records.
+    const FlatView t = stage_table<HOT>(tg, tg.at.ext[0], tg.at.enc_end);
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         uint32_t s[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) s[k] = __ldcs(slots + (uint64_t)k * slot_stride + i);
         uint4 w;
-        encode_record<HOT>(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
+        encode_record<HOT, HOT>(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
         __stcs(words + i, w);
     }
 }
@@ -122,7 +123,7 @@ template <class HOT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
-    const FlatView t = stage_table<HOT>(tg);
+    const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
     uint32_t tally[3] = {0, 0, 0};
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
@@ -144,7 +145,7 @@ synth_kernel(FlatView t, SynthView g, uint64_t first, uint64_t n, uint4* __restr
     const uint64_t step = (uint64_t)gridDim.x * kBlock;
     for (uint64_t i = (uint64_t)blockIdx.x * kBlock + threadIdx.x; i < n; i += step) {
         uint32_t f = FORM_NONE, c = 0, s[8] = {0, 0, 0, 0, 0, 0, 0, 0}, w[4];
-        if (synth_record(t, g, first + i, &f, s, &c, w)) encode_record<HotGlobal>(t, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+        if (synth_record(t, g, first + i, &f, s, &c, w)) encode_record<HotGlobal, HotGlobal>(t, f, s, c, &w[0], &w[1], &w[2], &w[3]);
         else c = ctrl_from_raw(w[0], w[3]);
         if (words) words[i] = make_uint4(w[0], w[1], w[2], w[3]);
         if (form) form[i] = (uint16_t)f;
@@ -177,7 +178,8 @@ struct DeviceState {
     int device = -1;
     int sm_count = 0;
     bool shared_ok = false;   // the hot part of the table fits the opt-in shared memory of this device
-    uint32_t hot_bytes = 0;
+    uint32_t hot_bytes = 0;   // decode window of the table
+    uint32_t enc_bytes = 0;   // encode window
     FlatView view{};
     std::vector<void*> table_allocs;
     unsigned long long* counters = nullptr;   // kCounterSlots x CNT_WORDS
@@ -186,7 +188,8 @@ struct DeviceState {
     // Grow-only staging for the host-memory paths.
     void* stage = nullptr;
     uint64_t stage_bytes = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr, stream2 = nullptr;
+    cudaEvent_t event = nullptr;
     std::mutex stage_mu;
     // Device address of g_static_scratch on this device, looked up on first use.
     unsigned char* static_scratch = nullptr;
@@ -278,7 +281,7 @@ void launch_decode(const DeviceState* d, cudaStream_t s, const uint4* words, uin
 void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, const uint32_t* slots, uint64_t stride,
                    const uint32_t* ctrl, uint64_t n, uint4* words) {
     if (use_shared(d, n))
-        encode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, form, slots, stride, ctrl, n, words);
+        encode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->enc_bytes, s>>>(d->view, form, slots, stride, ctrl, n, words);
     else
         encode_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, form, slots, stride, ctrl, n, words);
 }
@@ -357,32 +360,57 @@ constexpr uint64_t kChunkWords = 1ull << 22;   // host paths stream the batch in
 
 uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-// Host-memory decode of words [begin, end) on one device, chunked through its staging area.
+// Host-memory decode of words [begin, end) on one device.  The range is cut into chunks that
+// alternate between two halves of the staging area and two streams, so the copy-in of one
+// chunk, the kernel of another and the copy-out of a third overlap (the PCIe link is full
+// duplex); with pinned host buffers every copy is asynchronous.
 int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t n_total, uint64_t begin,
                       uint64_t end, uint16_t* form, uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
     std::lock_guard<std::mutex> g(d->stage_mu);
     CU_TRY(ctx, cudaSetDevice(d->device));
     const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
     const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
-    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
-    int rc = ensure_stage(ctx, d, total);
+    const uint64_t o_ctrl = o_slots + chunk * 32, half = align_up(o_ctrl + chunk * 4, 256);
+    const bool two = end - begin > chunk;
+    int rc = ensure_stage(ctx, d, two ? 2 * half : half);
     if (rc) return rc;
-    uint8_t* st = (uint8_t*)d->stage;
-    for (uint64_t at = begin; at < end; at += chunk) {
-        const uint64_t m = std::min(chunk, end - at);
-        CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
-        rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
-            launch_decode(d, d->stream, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), chunk,
-                          (uint32_t*)(st + o_ctrl), dc);
-        });
-        if (rc) return rc;
-        CU_TRY(ctx, cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
-        for (int k = 0; k < 8; ++k)
-            CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)k * n_total + at, st + o_slots + (uint64_t)k * chunk * 4, m * 4,
-                                        cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    int slot = -1;
+    unsigned long long* dc = nullptr;
+    if (counts) {
+        slot = take_counter_slot(d);
+        if (slot < 0) return fail(ctx, CUBIT_ERR_NOMEM, "too many counted calls in flight on one device");
+        dc = d->counters + (size_t)slot * CNT_WORDS;
     }
+    cudaStream_t streams[2] = {d->stream, d->stream2};
+    cudaError_t e = cudaSuccess;
+    if (dc) {
+        e = cudaMemsetAsync(dc, 0, sizeof(unsigned long long) * CNT_WORDS, streams[0]);
+        if (e == cudaSuccess) e = cudaEventRecord(d->event, streams[0]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(streams[1], d->event, 0);
+    }
+    uint64_t k = 0;
+    for (uint64_t at = begin; at < end && e == cudaSuccess; at += chunk, ++k) {
+        const uint64_t m = std::min(chunk, end - at);
+        cudaStream_t s = streams[k & 1];
+        uint8_t* st = (uint8_t*)d->stage + (k & 1) * half;
+        e = cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) break;
+        launch_decode(d, s, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), chunk,
+                      (uint32_t*)(st + o_ctrl), dc);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, s);
+        for (int p = 0; p < 8 && e == cudaSuccess; ++p)
+            e = cudaMemcpyAsync(slots + (uint64_t)p * n_total + at, st + o_slots + (uint64_t)p * chunk * 4, m * 4,
+                                cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, s);
+    }
+    unsigned long long host[CNT_WORDS] = {0, 0, 0, 0, 0};
+    if (e == cudaSuccess) e = cudaStreamSynchronize(streams[1]);
+    if (e == cudaSuccess && dc) e = cudaMemcpyAsync(host, dc, sizeof host, cudaMemcpyDeviceToHost, streams[0]);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(streams[0]);
+    if (slot >= 0) give_counter_slot(d, slot);
+    if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string("host decode: ") + cudaGetErrorString(e));
+    if (counts) add_counts(counts, host);
     return CUBIT_OK;
 }
 
@@ -530,17 +558,20 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         if (rc) return rc;
         d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
         d->hot_bytes = ft.at.hot_words * 4;
+        d->enc_bytes = (ft.at.enc_end - ft.at.ext[0]) * 4;
         int optin = 0;
         CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
-        d->shared_ok = (int)d->hot_bytes + 1024 <= optin;
+        d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
         if (d->shared_ok) {
             CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-            CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+            CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
             CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         }
         CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
         for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
         CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+        CU_TRY(c, cudaStreamCreateWithFlags(&d->stream2, cudaStreamNonBlocking));
+        CU_TRY(c, cudaEventCreateWithFlags(&d->event, cudaEventDisableTiming));
         ctx->devs.push_back(std::move(d));
     }
     *out = ctx.release();
@@ -556,6 +587,8 @@ extern "C" void cubit_ctx_destroy(cubit_ctx* ctx) {
         if (d->counters) cudaFree(d->counters);
         if (d->stage) cudaFree(d->stage);
         if (d->stream) cudaStreamDestroy(d->stream);
+        if (d->stream2) cudaStreamDestroy(d->stream2);
+        if (d->event) cudaEventDestroy(d->event);
     }
     delete ctx;
 }

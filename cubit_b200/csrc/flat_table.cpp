@@ -700,8 +700,10 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     for (size_t q = 0; q < 2; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
+    for (size_t q = 0; q < 2; ++q) L.var[q] = place(quad_plane(ft.var, VR_WORDS, q));
+    while (ft.blob.size() % 4) ft.blob.push_back(0);
+    L.enc_end = uint32_t(ft.blob.size());
     L.flagbest = place(ft.flagbest);
-    L.var = place(ft.var);
     L.gfields = place(ft.gfields);
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.total_words = uint32_t(ft.blob.size());

@@ -61,12 +61,12 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 19 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout19) {
+// The compiled table blob and its section offsets (BlobLayout as 21 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout21) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 19 * sizeof(uint32_t), "layout size");
-    memcpy(layout19, &m->flat.at, sizeof(BlobLayout));
+    static_assert(sizeof(BlobLayout) == 21 * sizeof(uint32_t), "layout size");
+    memcpy(layout21, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
 void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_classes, uint8_t* n_match, uint8_t* depth) {
@@ -168,7 +168,7 @@ void mir_encode_batch(void* h, const uint16_t* form, const uint32_t* slots, cons
         for (uint64_t i = b; i < e; ++i) {
             uint32_t s[8];
             for (int k = 0; k < 8; ++k) s[k] = slots[(uint64_t)k * n + i];
-            encode_record<HotPlain>(m->view, form[i], s, ctrl[i], &words[4 * i], &words[4 * i + 1], &words[4 * i + 2], &words[4 * i + 3]);
+            encode_record<HotPlain, HotPlain>(m->view, form[i], s, ctrl[i], &words[4 * i], &words[4 * i + 1], &words[4 * i + 2], &words[4 * i + 3]);
         }
     });
 }
@@ -187,7 +187,7 @@ void mir_synth_batch(void* h, uint32_t mix, uint64_t seed, uint32_t noise_ppm, u
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; ++i) {
             uint32_t f = FORM_NONE, c = 0, s[8] = {0}, w[4];
-            if (synth_record(m->view, g, first + i, &f, s, &c, w)) encode_record<HotPlain>(m->view, f, s, c, &w[0], &w[1], &w[2], &w[3]);
+            if (synth_record(m->view, g, first + i, &f, s, &c, w)) encode_record<HotPlain, HotPlain>(m->view, f, s, c, &w[0], &w[1], &w[2], &w[3]);
             else c = ctrl_from_raw(w[0], w[3]);
             memcpy(words + 4 * i, w, 16);
             if (form) form[i] = (uint16_t)f;
