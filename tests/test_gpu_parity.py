@@ -277,3 +277,27 @@ def test_decode_kernel_and_multi_kernel_cubin(codec, oracle, tmp_path):
     with pytest.raises(OSError, match="load error"):
         codec.decode_kernel(tmp_path / "missing.cubin", "k")
     del rng
+
+
+def test_multi_device_context_shards_host_batches(oracle):
+    """One process, two GPUs: host batches are cut into contiguous ranges, one per device, no exchange step."""
+    torch = pytest.importorskip("torch")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    both = cubit_b200.Codec(devices=(0, 1))
+    n = 300001
+    words = oracle.synth(MIX_ZIPF, 13, n, noise_ppm=10000, records=False)
+    d = both.decode_batch(words)
+    od = oracle.decode_batch(words, threads=T)
+    assert_records_equal(d[:3], od)
+    assert d[3]["n_decoded"] + d[3]["n_rejected"] == n
+    assert (both.encode_batch(*d[:3]) == oracle.encode_batch(*od, threads=T)).all()
+    status, rc = both.roundtrip_batch(words)
+    assert (status == oracle.roundtrip_batch(words, threads=T)).all()
+    assert rc["n_exact"] + rc["n_mismatch"] + rc["n_rejected"] == n
+    # a multi-kernel cubin is cut on the cumulative word count
+    kernels = [(f"k{k:05d}", oracle.synth(MIX_FAMILY, 50 + k, 4000 + 37 * k, records=False).tobytes()) for k in range(9)]
+    image = cubit_b200.build_cubin(kernels)
+    sections, word_start, form, slots, ctrl, raw, counts = both.decode_elf(image)
+    assert_records_equal((form, slots, ctrl), oracle.decode_batch(raw, threads=T))
+    both.close()
