@@ -43,6 +43,90 @@ WORKLOADS = {
                           "random words, one status byte out"},
 }
 METRIC = WORKLOADS["decode"]["metric"]
+
+
+def run_cubin(args, rank, world, local):
+    """cfg4: a synthetic multi-kernel cubin per GPU (kernel lengths lognormal(ln 20000, 1.0) clamped to
+    [2000, 200000] words, MMA-heavy family mix), every word of every kernel decoded by ONE launch through
+    cubit_decode_elf.  Host buffers in and out, so the number includes the copies over PCIe."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import cubit_b200
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    codec = cubit_b200.Codec(devices=(local,))
+    rng = np.random.default_rng(1000 + rank)
+    lengths = np.clip(np.exp(rng.normal(np.log(20000.0), 1.0, args.kernels)), 2000, 200000).astype(np.int64)
+    total = int(lengths.sum())
+    first = rank * (1 << 34)     # ranks draw disjoint ranges of one family-mix stream
+    words = codec.synth(cubit_b200.MIX_FAMILY, STREAM_SEED, total, first=first)[0]
+    starts = np.concatenate([[0], np.cumsum(lengths)])
+    kernels = [(f"k{rank:02d}_{k:05d}", words[starts[k]:starts[k + 1]].tobytes()) for k in range(args.kernels)]
+    image = cubit_b200.build_cubin(kernels)
+    del kernels
+    # Pinned host buffers, allocated once: the image, the records and the raw words.
+    lib, ctx = codec._lib, codec._ctx
+    n_out = int(((lengths + 7) // 8 * 8).sum())
+
+    def pinned(nbytes, dtype, shape):
+        p = C.c_void_p()
+        codec._check(lib.cubit_host_alloc(ctx, nbytes, C.byref(p)))
+        return p, np.ctypeslib.as_array(C.cast(p, C.POINTER(dtype)), shape=shape)
+    p_img, img = pinned(len(image), C.c_uint8, (len(image),))
+    img[:] = np.frombuffer(image, np.uint8)
+    p_form, form = pinned(n_out * 2, C.c_uint16, (n_out,))
+    p_slots, slots = pinned(n_out * 32, C.c_uint32, (8, n_out))
+    p_ctrl, ctrl = pinned(n_out * 4, C.c_uint32, (n_out,))
+    p_raw, raw = pinned(n_out * 16, C.c_uint8, (n_out, 16))
+    word_start = np.zeros(args.kernels + 1, np.uint64)
+    counts = cubit_b200._native.Counts()
+    times = []
+    for it in range(args.warmup + args.steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        elf = C.c_void_p()
+        codec._check(lib.cubit_elf_parse(p_img, len(image), C.byref(elf)))
+        assert lib.cubit_elf_num_text(elf) == args.kernels
+        codec._check(lib.cubit_decode_elf(ctx, elf, None, args.kernels, C.c_void_p(word_start.ctypes.data), n_out, p_form, p_slots,
+                                          p_ctrl, p_raw if it == 0 else None, C.byref(counts)))
+        lib.cubit_elf_free(elf)
+        dt = time.perf_counter() - t0
+        if it == 0:
+            # padding: every section is a multiple of 8 words (NOPs, then one self-branch)
+            assert int(word_start[-1]) == n_out
+            sample = np.arange(0, n_out, 4099)
+            sys.path.insert(0, str(ROOT / "oracle"))
+            from oracle_lib import Oracle
+            of, os_, oc = Oracle().decode_batch(raw[sample])
+            assert (form[sample] == of).all() and (slots[:, sample] == os_).all() and (ctrl[sample] == oc).all()
+        if it >= args.warmup:
+            times.append(dt)
+    counts = counts.as_dict()
+    t = torch.tensor([sum(times)], dtype=torch.float64, device=torch.device("cuda", local))
+    nw = torch.tensor([float(word_start[-1])], dtype=torch.float64, device=torch.device("cuda", local))
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nw, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        sec = float(t.item()) / args.steps
+        value = float(nw.item()) / sec / 1e9
+        line = {"metric": "decode_kernel_cubin_throughput", "value": value, "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+                "config": {"workload": "cfg4 multi-kernel cubin: parse + one decode launch per GPU over all kernels; pinned host "
+                                       "buffers in and out", "kernels_per_gpu": args.kernels,
+                           "words_per_gpu": int(word_start[-1]), "image_bytes": len(image), "sections": 9 + 4 * args.kernels},
+                "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": int(word_start[-1]) * 16,
+                        "d2h_bytes_per_step": int(word_start[-1]) * 38},
+                "gpu_launches": args.steps, "counts": counts}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 DEFAULT_WORDS = 64 * 1024 * 1024    # 1 GiB of 16-byte words
 STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
@@ -215,7 +299,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--words", type=int, default=DEFAULT_WORDS, help="words per GPU per step")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS),
+    ap.add_argument("--kernels", type=int, default=1000, help="cubin workload: kernels per GPU (cfg4 uses 10000 in all)")
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS) + ["cubin"],
                     help="decode is the headline (cfg1); encode / roundtrip report the other two kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
@@ -225,6 +310,10 @@ def main():
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+
+    if args.workload == "cubin":
+        run_cubin(args, rank, world, local)
         return
 
     import numpy as np

@@ -301,3 +301,35 @@ def test_multi_device_context_shards_host_batches(oracle):
     sections, word_start, form, slots, ctrl, raw, counts = both.decode_elf(image)
     assert_records_equal((form, slots, ctrl), oracle.decode_batch(raw, threads=T))
     both.close()
+
+
+def test_large_host_batch_crosses_chunk_and_stream_boundaries(codec, oracle):
+    """Host batches above 4 Mi words are streamed in chunks over two staging halves and two streams:
+    every plane must equal the device-path result, and the oracle on a strided sample and around the seams."""
+    torch = pytest.importorskip("torch")
+    n = 9 * 1024 * 1024 + 12345
+    words, gform, gslots, gctrl = codec.synth(MIX_ZIPF, 3, n, noise_ppm=10000)
+    form, slots, ctrl, counts = codec.decode_batch(words)
+    dev = torch.device("cuda", 0)
+    dw = torch.from_numpy(words.reshape(-1)).to(dev)
+    dform = torch.empty(n, dtype=torch.int16, device=dev)
+    dslots = torch.empty(8 * n, dtype=torch.int32, device=dev)
+    dctrl = torch.empty(n, dtype=torch.int32, device=dev)
+    dcounts = codec.decode_device(dw.data_ptr(), n, dform.data_ptr(), dslots.data_ptr(), dctrl.data_ptr(), want_counts=True)
+    torch.cuda.synchronize()
+    assert counts == dcounts
+    assert (form == dform.cpu().numpy().view(np.uint16)).all()
+    assert (slots == dslots.cpu().numpy().view(np.uint32).reshape(8, n)).all()
+    assert (ctrl == dctrl.cpu().numpy().view(np.uint32)).all()
+    chunk = 4 * 1024 * 1024
+    idx = np.unique(np.concatenate([np.arange(0, n, 97), np.arange(chunk - 64, chunk + 64),
+                                    np.arange(2 * chunk - 64, 2 * chunk + 64), np.arange(n - 64, n)]))
+    of, os_, oc = oracle.decode_batch(words[idx], threads=T)
+    assert (form[idx] == of).all() and (slots[:, idx] == os_).all() and (ctrl[idx] == oc).all()
+    # encode and roundtrip through the host path at the same size
+    enc = codec.encode_batch(gform, gslots, gctrl)
+    keep = gform != 0xFFFF
+    assert (enc[keep] == words[keep]).all() and not enc[~keep].any()
+    status, rc = codec.roundtrip_batch(words)
+    assert (status[idx] == oracle.roundtrip_batch(words[idx], threads=T)).all()
+    assert rc["n_rejected"] == counts["n_rejected"] and rc["n_exact"] + rc["n_mismatch"] == counts["n_decoded"]
