@@ -131,8 +131,8 @@ DEFAULT_WORDS = 64 * 1024 * 1024    # 1 GiB of 16-byte words
 STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per decoded word from the ncu capture summarised in
-# profiles/decode_kernel_zipf.md (null until a capture exists).
-NCU_DRAM_BYTES_PER_WORD = None
+# profiles/decode_kernel_zipf.md: (268.7 MB + 580.7 MB) / 16 Mi words of the captured launch.
+NCU_DRAM_BYTES_PER_WORD = 50.6
 
 
 def env_int(name, default):
@@ -186,7 +186,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def oracle_rate(words_np, threads, budget_s=15.0):
+def oracle_rate(words_np, threads, seconds=15.0):
     """Oracle decode throughput (insn/s) on a bounded prefix of `words_np`."""
     sys.path.insert(0, str(ROOT / "oracle"))
     from oracle_lib import Oracle
@@ -195,7 +195,7 @@ def oracle_rate(words_np, threads, budget_s=15.0):
     t0 = time.perf_counter()
     o.decode_batch(words_np[:probe], threads=threads)
     rate = probe / max(time.perf_counter() - t0, 1e-6)
-    n = int(max(probe, min(len(words_np), rate * budget_s)))
+    n = int(max(probe, min(len(words_np), rate * seconds)))
     t0 = time.perf_counter()
     o.decode_batch(words_np[:n], threads=threads)
     dt = time.perf_counter() - t0
