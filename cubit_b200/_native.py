@@ -22,6 +22,11 @@ class FieldInfo(C.Structure):
                 ("stored_bits", C.c_uint32), ("name", C.c_char_p), ("extraction", C.c_char_p)]
 
 
+class KernelMeta(C.Structure):
+    _fields_ = [("regcount", C.c_uint32), ("num_barriers", C.c_uint32), ("max_reg", C.c_uint32),
+                ("barrier_mask", C.c_uint32), ("first_exit", C.c_uint64), ("n_exits", C.c_uint64)]
+
+
 class VariantInfo(C.Structure):
     _fields_ = [("key", C.c_char_p), ("mod_group", C.c_char_p), ("opcode", C.c_char_p), ("key_id", C.c_uint32),
                 ("layout_kind", C.c_uint32), ("synth_mask", C.c_uint32), ("ra_tok", C.c_int32), ("rb_tok", C.c_int32),
@@ -56,6 +61,8 @@ SIGNATURES = {
     "cubit_elf_find": (C.c_int, [C.c_void_p, C.c_char_p, u32p]),
     "cubit_decode_elf": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Counts)]),
+    "cubit_infer_kernel_meta": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(KernelMeta), C.c_void_p,
+                                          C.c_uint64, u64p]),
     "cubit_elf_build": (C.c_int, [C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), u64p, C.c_uint32, C.c_void_p, C.c_uint64,
                                   u64p]),
 }

@@ -321,6 +321,42 @@ class Codec:
         finally:
             self._lib.cubit_elf_free(elf)
 
+    def infer_kernel_meta(self, data: bytes, kernel_name: str | None = None) -> list[dict]:
+        """Per text section of a cubin image (or only the first whose name contains `kernel_name`): the
+        metadata the reference infers from code (src/main.rs:787-867) — regcount, num_barriers and the byte
+        offsets of EXIT instructions — from one GPU launch over all sections."""
+        buf = np.frombuffer(data, np.uint8)
+        elf = C.c_void_p()
+        if self._lib.cubit_elf_parse(_ptr(buf), len(buf), C.byref(elf)):
+            raise OSError("load error: " + self._lib.cubit_last_error(None).decode())
+        try:
+            names = []
+            for i in range(self._lib.cubit_elf_num_text(elf)):
+                name = C.c_char_p()
+                self._lib.cubit_elf_text(elf, i, name, None, None)
+                names.append(name.value.decode())
+            indices = None
+            if kernel_name is not None:
+                idx = C.c_uint32()
+                if self._lib.cubit_elf_find(elf, kernel_name.encode(), idx):
+                    listed = ", ".join('"' + s + '"' for s in names)
+                    raise ValueError(f"kernel '{kernel_name}' not found. Available: [{listed}]")
+                indices = np.array([idx.value], np.uint32)
+                names = [names[idx.value]]
+            k = len(names)
+            meta = (_native.KernelMeta * max(k, 1))()
+            total = C.c_uint64()
+            self._check(self._lib.cubit_infer_kernel_meta(self._ctx, elf, _ptr(indices), k, meta, None, 0, C.byref(total)))
+            exits = np.zeros(max(total.value, 1), np.uint32)
+            self._check(self._lib.cubit_infer_kernel_meta(self._ctx, elf, _ptr(indices), k, meta, _ptr(exits), len(exits),
+                                                          C.byref(total)))
+            return [dict(name=names[i], regcount=meta[i].regcount, num_barriers=meta[i].num_barriers,
+                         max_reg=meta[i].max_reg, barrier_mask=meta[i].barrier_mask,
+                         exit_offsets=exits[meta[i].first_exit:meta[i].first_exit + meta[i].n_exits].tolist())
+                    for i in range(k)]
+        finally:
+            self._lib.cubit_elf_free(elf)
+
     def decode_kernel(self, cubin_path: str | os.PathLike, kernel_name: str) -> list[dict]:
         """cubit.decode_kernel(cubin_path, kernel_name) (reference src/python.rs:104-169)."""
         try:

@@ -41,6 +41,7 @@ struct FlatTable {
     std::vector<uint32_t> ext;       // XR_WORDS per variant
     std::vector<uint32_t> var;       // VR_WORDS per variant
     std::vector<uint32_t> gfields;
+    std::vector<uint32_t> metaf;     // MF_WORDS per variant
     std::vector<VariantMeta> meta;
     uint32_t n_keys = 0;
     uint32_t n_buckets = 0;

@@ -188,6 +188,25 @@ int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indic
                      uint64_t* word_start, uint64_t capacity, uint16_t* form, uint32_t* slots,
                      uint32_t* ctrl, void* raw_words, cubit_counts* counts);
 
+typedef struct {
+    uint32_t regcount;      /* (max_reg + 32) & ~31, at least 32: registers are allocated in blocks of 32 */
+    uint32_t num_barriers;  /* distinct BSSY barrier indices */
+    uint32_t max_reg;       /* largest register number below 255 named by the code */
+    uint32_t barrier_mask;  /* bit b set: barrier b is used */
+    uint64_t first_exit;    /* index of this kernel's first entry in exit_offsets */
+    uint64_t n_exits;       /* number of EXIT instructions */
+} cubit_kernel_meta;
+
+/* Replaces infer_kernel_meta (reference src/main.rs:787-867) for many kernels at once: one
+ * launch decodes every word of the chosen text sections (indices == NULL: all) and reduces,
+ * per kernel, the largest register number, the BSSY barrier set and the EXIT positions; words
+ * that match no variant use the reference's raw-bits fallback.  exit_offsets (optional)
+ * receives the byte offsets of EXIT instructions inside their section, kernel by kernel in
+ * ascending order; *n_exits is their total (call with exit_offsets == NULL to size it). */
+int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indices, uint32_t n_sections,
+                            cubit_kernel_meta* meta, uint32_t* exit_offsets, uint64_t exit_capacity,
+                            uint64_t* n_exits);
+
 /* Synthetic multi-kernel cubin with the section layout of the reference's Mercury-free
  * builder (src/elf_builder.rs:535-847): 9 + 4N sections, one ".text.<name>" per kernel,
  * 128-byte aligned and padded with NOPs plus one trailing self-branch.  Note and info

@@ -40,6 +40,9 @@ class Oracle:
         L.orc_decode_full.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint32), C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32), C.c_void_p,
                                       C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+        L.orc_variant_opcode.argtypes = [C.c_void_p, C.c_uint32, C.c_char_p, C.c_uint32]
+        L.orc_kernel_meta.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                      C.c_void_p, C.c_uint32]
         L.orc_field_extraction.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_char_p, C.c_uint32]
         L.orc_decode_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         L.orc_encode_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_int]
@@ -90,9 +93,20 @@ class Oracle:
             self.lib.orc_field_extraction(self.h, variant.value, i, buf, 64)
             fields.append(dict(shift=int(sh[i]), bits=int(bits[i]), value=int(vals[i]), token_idx=int(tok[i]),
                                extraction=buf.value.decode()))
-        out.update(variant=variant.value, key=key, mod_group=mg, fields=fields, synth=synth.value, tie=bool(tie.value),
+        self.lib.orc_variant_opcode(self.h, variant.value, buf, 64)
+        out.update(variant=variant.value, key=key, mod_group=mg, opcode=buf.value.decode(), fields=fields, synth=synth.value, tie=bool(tie.value),
                    score=C.c_int32(score.value).value)
         return out
+
+    def kernel_meta(self, code: bytes):
+        """Reference metadata inference over one kernel's code: regcount, num_barriers, exit offsets."""
+        buf = np.frombuffer(code, np.uint8)
+        cap = max(len(buf) // 16, 1)
+        exits = np.zeros(cap, np.uint32)
+        mr, bm = C.c_uint32(), C.c_uint32()
+        n = self.lib.orc_kernel_meta(self.h, buf.ctypes.data if len(buf) else None, len(buf), mr, bm, exits.ctypes.data, cap)
+        return dict(max_reg=mr.value, barrier_mask=bm.value, regcount=max(((mr.value + 32) & ~31), 32),
+                    num_barriers=bin(bm.value).count("1"), exit_offsets=exits[:n].tolist())
 
     def decode_batch(self, words: np.ndarray, threads: int = 1):
         words = np.ascontiguousarray(words, dtype=np.uint8).reshape(-1, 16)

@@ -61,12 +61,12 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 21 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout21) {
+// The compiled table blob and its section offsets (BlobLayout as 22 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout22) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 21 * sizeof(uint32_t), "layout size");
-    memcpy(layout21, &m->flat.at, sizeof(BlobLayout));
+    static_assert(sizeof(BlobLayout) == 22 * sizeof(uint32_t), "layout size");
+    memcpy(layout22, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
 void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_classes, uint8_t* n_match, uint8_t* depth) {
@@ -149,6 +149,14 @@ void mir_rank_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* loop_le
             if (mm == (1u << f)) mm = 0;
         }
         loop_len[i] = (uint8_t)__builtin_popcount(mm);
+    }
+}
+void mir_word_meta(void* h, const uint32_t* words, uint64_t n, uint32_t* max_reg, uint32_t* barriers, uint8_t* is_exit) {
+    const Mirror* m = (const Mirror*)h;
+    for (uint64_t i = 0; i < n; ++i) {
+        uint32_t ex;
+        word_meta<HotPlain>(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], &max_reg[i], &barriers[i], &ex);
+        is_exit[i] = (uint8_t)ex;
     }
 }
 void mir_decode_batch(void* h, const uint32_t* words, uint64_t n, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int threads) {

@@ -56,6 +56,12 @@ def mirror():
             lib.mir_synth_batch(h, mix, C.c_uint64(seed), noise, C.c_uint64(first), C.c_uint64(n), C.c_void_p(words.ctypes.data),
                                 C.c_void_p(form.ctypes.data), C.c_void_p(slots.ctypes.data), C.c_void_p(ctrl.ctypes.data), T)
             return words, form, slots, ctrl
+        def word_meta(self, words):
+            n = len(words)
+            mr = np.zeros(n, np.uint32); bm = np.zeros(n, np.uint32); ex = np.zeros(n, np.uint8)
+            lib.mir_word_meta(h, C.c_void_p(words.ctypes.data), C.c_uint64(n), C.c_void_p(mr.ctypes.data),
+                              C.c_void_p(bm.ctypes.data), C.c_void_p(ex.ctypes.data))
+            return mr, bm, ex
     return M()
 
 
@@ -86,3 +92,16 @@ def test_core_matches_oracle_on_adversarial_words(mirror, oracle):
     ctrl = rng.integers(0, 2**32, size=len(form), dtype=np.uint32)
     form[::97] = 0xFFFF
     assert (oracle.encode_batch(form, slots, ctrl, threads=T) == mirror.encode(form, slots, ctrl)).all()
+
+
+def test_kernel_meta_core_matches_oracle(mirror, oracle):
+    words = oracle.synth(MIX_FAMILY, 5, 100000, noise_ppm=50000, threads=T, records=False)
+    mr, bm, ex = mirror.word_meta(words)
+    exits = 0
+    for k in range(0, len(words), 5000):
+        want = oracle.kernel_meta(words[k:k + 5000].tobytes())
+        assert want["max_reg"] == int(mr[k:k + 5000].max())
+        assert want["barrier_mask"] == int(np.bitwise_or.reduce(bm[k:k + 5000]))
+        assert want["exit_offsets"] == (np.nonzero(ex[k:k + 5000])[0] * 16).tolist()
+        exits += len(want["exit_offsets"])
+    assert exits > 50
