@@ -42,6 +42,7 @@ struct FlatTable {
     std::vector<uint32_t> var;       // VR_WORDS per variant
     std::vector<uint32_t> gfields;
     std::vector<uint32_t> metaf;     // MF_WORDS per variant
+    std::vector<uint32_t> rt;        // 8 per variant: roundtrip constants
     std::vector<VariantMeta> meta;
     uint32_t n_keys = 0;
     uint32_t n_buckets = 0;

@@ -61,12 +61,12 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 22 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout22) {
+// The compiled table blob and its section offsets (BlobLayout as 24 u32).
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout24) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 22 * sizeof(uint32_t), "layout size");
-    memcpy(layout22, &m->flat.at, sizeof(BlobLayout));
+    static_assert(sizeof(BlobLayout) == 24 * sizeof(uint32_t), "layout size");
+    memcpy(layout24, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
 void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_classes, uint8_t* n_match, uint8_t* depth) {
@@ -185,6 +185,13 @@ void mir_roundtrip_batch(void* h, const uint32_t* words, uint64_t n, uint8_t* st
     pfor(n, threads, [=](uint64_t b, uint64_t e) {
         for (uint64_t i = b; i < e; ++i)
             status[i] = (uint8_t)roundtrip_word<HotPlain>(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+    });
+}
+void mir_roundtrip_unfused_batch(void* h, const uint32_t* words, uint64_t n, uint8_t* status, int threads) {
+    const Mirror* m = (const Mirror*)h;
+    pfor(n, threads, [=](uint64_t b, uint64_t e) {
+        for (uint64_t i = b; i < e; ++i)
+            status[i] = (uint8_t)roundtrip_word_unfused<HotPlain>(m->view, words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
     });
 }
 void mir_synth_batch(void* h, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first, uint64_t n, uint32_t* words,

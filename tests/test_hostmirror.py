@@ -50,6 +50,11 @@ def mirror():
             lib.mir_roundtrip_batch(h, C.c_void_p(words.ctypes.data), C.c_uint64(len(words)), C.c_void_p(st.ctypes.data), T)
             return st
 
+        def roundtrip_unfused(self, words):
+            st = np.zeros(len(words), np.uint8)
+            lib.mir_roundtrip_unfused_batch(h, C.c_void_p(words.ctypes.data), C.c_uint64(len(words)), C.c_void_p(st.ctypes.data), T)
+            return st
+
         def synth(self, mix, seed, n, noise=0, first=0):
             words = np.zeros((n, 16), np.uint8); form = np.zeros(n, np.uint16)
             slots = np.zeros((8, n), np.uint32); ctrl = np.zeros(n, np.uint32)
@@ -105,3 +110,18 @@ def test_kernel_meta_core_matches_oracle(mirror, oracle):
         assert want["exit_offsets"] == (np.nonzero(ex[k:k + 5000])[0] * 16).tolist()
         exits += len(want["exit_offsets"])
     assert exits > 50
+
+
+def test_fused_roundtrip_equals_decode_encode_compare(mirror, oracle):
+    """The roundtrip kernel checks (w & ~M) == A per variant instead of building and re-encoding a record;
+    it must agree with the spelled-out decode -> encode -> compare and with the oracle on every word."""
+    words = np.concatenate([adversarial_words(np.random.default_rng(7), 25),
+                            oracle.synth(MIX_UNIFORM, 9, 200000, noise_ppm=100000, threads=T, records=False)])
+    # flip bits everywhere, including the scheduling field and the reuse bits of the upper word
+    rng = np.random.default_rng(8)
+    words = words.copy()
+    words[::3, 12:16] ^= rng.integers(0, 256, size=(len(words[::3]), 4), dtype=np.uint8)
+    fused, unfused = mirror.roundtrip(words), mirror.roundtrip_unfused(words)
+    assert (fused == unfused).all()
+    assert (fused == oracle.roundtrip_batch(words, threads=T)).all()
+    assert np.bincount(fused, minlength=3).min() > 1000
