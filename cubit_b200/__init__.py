@@ -3,9 +3,11 @@
 Module-level functions carry the names and signatures of the reference's PyO3 module
 (reference src/python.rs:215-225): ``decode``, ``decode_kernel``, ``table_info`` run on the
 GPU through a process-wide :class:`Codec` created on first use (the reference keeps a
-process-wide table and index the same way, src/python.rs:28-42).  ``encode``, ``to_sass`` and
-``asm`` work on SASS *text*; the text layer is not part of this package yet and they raise
-NotImplementedError — record-level encoding is :meth:`Codec.encode_batch`.
+process-wide table and index the same way, src/python.rs:28-42).  ``encode`` parses the text
+on the host, encodes the record on the GPU and applies the text-derived bits on the host;
+``encode_lines`` does the same for a program with labels.  ``to_sass`` (the printer) and
+``asm`` (which runs the reference's scheduling pass before encoding) are not part of this
+package and raise NotImplementedError.
 """
 from __future__ import annotations
 
@@ -17,7 +19,7 @@ from .codec import (FORM_NONE, MEM_DEVICE, MEM_HOST, MIX_FAMILY, MIX_UNIFORM, MI
 from .sharding import shard_range, shard_sections
 
 __all__ = ["Codec", "CubitError", "FieldMeta", "VariantMeta", "build_cubin", "unpack_ctrl", "shard_range",
-           "shard_sections", "decode", "decode_kernel", "table_info", "encode", "to_sass", "asm", "FORM_NONE",
+           "shard_sections", "decode", "decode_kernel", "table_info", "encode", "encode_lines", "to_sass", "asm", "FORM_NONE",
            "MEM_HOST", "MEM_DEVICE", "MIX_UNIFORM", "MIX_ZIPF", "MIX_FAMILY", "RT_EXACT", "RT_MISMATCH", "RT_REJECTED",
            "SCHED_MASK"]
 
@@ -51,9 +53,18 @@ def table_info() -> tuple:
     return default_codec().table_info()
 
 
-def encode(sass: str, addr: int = 0):
-    raise NotImplementedError("text-level encode needs the SASS parser, which this package does not include; "
-                              "use Codec.encode_batch on records")
+def encode(sass: str, addr: int = 0) -> tuple:
+    """Encode one SASS instruction to (lo64, hi64); ValueError("parse error: ..." /
+    "encode error: ...") as the reference raises."""
+    return default_codec().encode(sass, addr)
+
+
+def encode_lines(code: str, addr: int = 0) -> tuple:
+    """(bytes, count) for a program: ';' / newline separated statements, labels, comments and
+    optional "[B------:R-:W-:-:S01]" prefixes.  Control codes are taken as written; the
+    reference's asm() reschedules them first, which this function does not do."""
+    words = default_codec().encode_text(code, addr, program=True)
+    return words.tobytes(), len(words)
 
 
 def to_sass(lo: int, hi: int, addr: int = 0) -> str:
@@ -61,4 +72,5 @@ def to_sass(lo: int, hi: int, addr: int = 0) -> str:
 
 
 def asm(code: str, addr: int = 0):
-    raise NotImplementedError("the assembler front end is not part of this package")
+    raise NotImplementedError("asm() runs the reference's scheduling pass before encoding, which is not part of "
+                              "this package; encode_lines() assembles the same text with control codes as written")

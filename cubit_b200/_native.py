@@ -65,6 +65,10 @@ SIGNATURES = {
                                           C.c_uint64, u64p]),
     "cubit_elf_build": (C.c_int, [C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), u64p, C.c_uint32, C.c_void_p, C.c_uint64,
                                   u64p]),
+    "cubit_text_lower": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_int, C.c_uint64, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_void_p, u64p]),
+    "cubit_text_encode": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_int, C.c_uint64, C.c_void_p, u64p]),
+    "cubit_text_parse": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64, u64p]),
 }
 
 _lib = None

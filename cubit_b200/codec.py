@@ -24,6 +24,8 @@ FORM_NONE = 0xFFFF
 RT_EXACT, RT_MISMATCH, RT_REJECTED = 0, 1, 2
 SCHED_MASK = 0x1FFFF << 105
 NOT_STORED = 0xFFFFFFFF
+TEXT_ONE, TEXT_PROGRAM = 0, 1
+ERR_TEXT = -8
 STATIC_MAX_WORDS = 65536
 
 
@@ -282,6 +284,64 @@ class Codec:
             clean = (int(lo) & (2**64 - 1)) | ((int(hi) & 0xFFFFFFFF) << 64)
             raise ValueError(f"decode error: no instruction matches code 0x{clean:032x} at opcode 0x{opcode_bits:04x}")
         return self.record_to_dict(form[0], slots[:, 0], ctrl[0], addr)
+
+    # ---- SASS text (host parse, GPU record encode, host patch) ----------------------------
+
+    def parse_text(self, line: str, addr: int = 0) -> dict:
+        """The parsed form of one instruction line (key, opcode, guard, typed operands, ...);
+        ValueError("parse error: ...") when the line is not an instruction."""
+        import json
+        need = C.c_uint64()
+        text = line.encode()
+        rc = self._lib.cubit_text_parse(self._ctx, text, addr, None, 0, need)
+        if rc == ERR_TEXT:
+            raise ValueError(self._lib.cubit_last_error(self._ctx).decode())
+        self._check(rc)
+        buf = C.create_string_buffer(need.value)
+        self._check(self._lib.cubit_text_parse(self._ctx, text, addr, buf, need.value, need))
+        return json.loads(buf.value.decode())
+
+    def lower_text(self, text: str, addr: int = 0, program: bool = True):
+        """Text -> (form, slots, ctrl, clear, set): the records cubit_encode_batch takes and the
+        128-bit patches ((word & ~clear) | set) that carry the text-derived bits.  clear / set
+        are uint8[n, 16] little-endian.  ValueError with the reference's message on failure."""
+        mode = TEXT_PROGRAM if program else TEXT_ONE
+        raw = text.encode()
+        n = C.c_uint64()
+        rc = self._lib.cubit_text_lower(self._ctx, raw, addr, mode, 0, None, None, None, None, None, n)
+        if rc == ERR_TEXT:
+            raise ValueError(self._lib.cubit_last_error(self._ctx).decode())
+        self._check(rc)
+        cap = max(int(n.value), 1)
+        form = np.zeros(cap, np.uint16); slots = np.zeros((8, cap), np.uint32); ctrl = np.zeros(cap, np.uint32)
+        clear = np.zeros((cap, 16), np.uint8); set_ = np.zeros((cap, 16), np.uint8)
+        self._check(self._lib.cubit_text_lower(self._ctx, raw, addr, mode, cap, _ptr(form), _ptr(slots), _ptr(ctrl),
+                                               _ptr(clear), _ptr(set_), n))
+        k = int(n.value)
+        return form[:k], slots[:, :k], ctrl[:k], clear[:k], set_[:k]
+
+    def encode_text(self, text: str, addr: int = 0, program: bool = True) -> np.ndarray:
+        """Text -> uint8[n, 16] words.  `program=False`: one bare instruction, as the reference's
+        encode(sass, addr); `program=True`: statements with labels, comments and optional
+        control-code prefixes, as its assembler reads them (without its scheduling pass)."""
+        mode = TEXT_PROGRAM if program else TEXT_ONE
+        raw = text.encode()
+        n = C.c_uint64()
+        rc = self._lib.cubit_text_encode(self._ctx, raw, addr, mode, 0, None, n)
+        if rc == ERR_TEXT:
+            raise ValueError(self._lib.cubit_last_error(self._ctx).decode())
+        self._check(rc)
+        words = np.zeros((max(int(n.value), 1), 16), np.uint8)
+        rc = self._lib.cubit_text_encode(self._ctx, raw, addr, mode, len(words), _ptr(words), n)
+        if rc == ERR_TEXT:
+            raise ValueError(self._lib.cubit_last_error(self._ctx).decode())
+        self._check(rc)
+        return words[:int(n.value)]
+
+    def encode(self, sass: str, addr: int = 0) -> tuple[int, int]:
+        """cubit.encode(sass, addr=0) -> (lo, hi) (reference src/python.rs:48-60)."""
+        w = self.encode_text(sass, addr, program=False)[0].tobytes()
+        return int.from_bytes(w[:8], "little"), int.from_bytes(w[8:], "little")
 
     def decode_elf(self, data: bytes, kernel_name: str | None = None, want_raw: bool = True):
         """All words of the text sections of a cubin image (or of the first section whose name

@@ -27,6 +27,7 @@
 #include "codec_core.cuh"
 #include "elf_text.hpp"
 #include "flat_table.hpp"
+#include "sass_text.hpp"
 #include "isa_table.hpp"
 
 using namespace cubit;
@@ -249,6 +250,7 @@ struct cubit_ctx {
     std::mutex err_mu;
     std::map<std::thread::id, std::string> errors;
     std::mutex synth_mu;
+    std::unique_ptr<TextEncoder> text;   // built with the context; reads `table`
 };
 
 struct cubit_elf {
@@ -580,6 +582,7 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         return fail(nullptr, CUBIT_ERR_TABLE, std::string("table ") + path + ": " + e.what());
     }
     const FlatTable& ft = ctx->flat;
+    ctx->text.reset(new TextEncoder(ctx->table));
     ctx->field_infos.resize(ft.meta.size());
     for (size_t v = 0; v < ft.meta.size(); ++v) {
         ctx->by_name[{ft.meta[v].key, ft.meta[v].mod_group}] = (uint32_t)v;
@@ -1065,5 +1068,205 @@ extern "C" int cubit_elf_build(const char* const* names, const void* const* code
     } catch (const std::exception& e) {
         return fail(nullptr, CUBIT_ERR_ELF, e.what());
     }
+    return CUBIT_OK;
+}
+
+// ---- SASS text ---------------------------------------------------------------------------
+
+namespace {
+
+void put_bits(uint32_t slots[8], uint32_t pos, uint32_t nbits, uint64_t v) {
+    for (uint32_t done = 0; done < nbits;) {
+        const uint32_t limb = (pos + done) >> 5, off = (pos + done) & 31u;
+        const uint32_t take = std::min(32u - off, nbits - done);
+        const uint32_t mask = take == 32u ? 0xFFFFFFFFu : ((1u << take) - 1u);
+        slots[limb] = (slots[limb] & ~(mask << off)) | (((uint32_t)(v >> done) & mask) << off);
+        done += take;
+    }
+}
+
+struct LoweredBatch {
+    std::vector<uint16_t> form;
+    std::vector<uint32_t> slots;   // 8 per instruction, instruction-major here
+    std::vector<uint32_t> ctrl;
+    std::vector<u128> clear, set;
+};
+
+// Throws TextError carrying the message the reference would report.
+void lower_text(const cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, LoweredBatch* out) {
+    std::vector<TextInstruction> insns;
+    if (mode == CUBIT_TEXT_ONE) {
+        try {
+            insns.push_back(parse_sass(text, base_addr));
+        } catch (const TextError& e) {
+            throw TextError(std::string("parse error: ") + e.what());
+        }
+    } else {
+        insns = parse_program(text, base_addr);
+    }
+    for (const TextInstruction& insn : insns) {
+        LoweredInstruction low;
+        try {
+            low = ctx->text->lower(insn);
+        } catch (const TextError& e) {
+            if (mode == CUBIT_TEXT_ONE) throw TextError(std::string("encode error: ") + e.what());
+            char at[32];
+            snprintf(at, sizeof at, "0x%x", insn.addr);
+            throw TextError(std::string("encode error at addr ") + at + ": " + e.what());
+        }
+        uint32_t slots[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (!low.raw) {
+            const VariantMeta& m = ctx->flat.meta[low.variant];
+            for (size_t k = 0; k < m.fields.size(); ++k) {
+                const FieldMeta& f = m.fields[k];
+                if (f.dst_pos == 0xFFFFFFFFu) continue;
+                put_bits(slots, f.dst_pos, f.stored_bits, low.values[k]);
+            }
+        }
+        out->form.push_back(low.raw ? (uint16_t)0xFFFF : (uint16_t)low.variant);
+        out->slots.insert(out->slots.end(), slots, slots + 8);
+        out->ctrl.push_back(low.ctrl);
+        out->clear.push_back(low.clear);
+        out->set.push_back(low.set);
+    }
+}
+
+void json_escape(const std::string& s, std::string* out) {
+    *out += '"';
+    for (unsigned char c : s) {
+        if (c == '"' || c == '\\') { *out += '\\'; *out += (char)c; }
+        else if (c < 0x20) { char b[8]; snprintf(b, sizeof b, "\\u%04x", c); *out += b; }
+        else *out += (char)c;
+    }
+    *out += '"';
+}
+
+}  // namespace
+
+extern "C" int cubit_text_lower(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
+                                uint16_t* form, uint32_t* slots, uint32_t* ctrl, void* clear, void* set,
+                                uint64_t* n_out) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (!text || !n_out) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
+    if (mode != CUBIT_TEXT_ONE && mode != CUBIT_TEXT_PROGRAM) return fail(ctx, CUBIT_ERR_INVALID, "unknown text mode");
+    LoweredBatch b;
+    try {
+        lower_text(ctx, text, base_addr, mode, &b);
+    } catch (const TextError& e) {
+        return fail(ctx, CUBIT_ERR_TEXT, e.what());
+    } catch (const std::exception& e) {
+        return fail(ctx, CUBIT_ERR_INVALID, e.what());
+    }
+    const uint64_t n = b.form.size();
+    *n_out = n;
+    if (n > capacity || !form || !slots || !ctrl || !clear || !set) return CUBIT_OK;
+    for (uint64_t i = 0; i < n; ++i) {
+        form[i] = b.form[i];
+        ctrl[i] = b.ctrl[i];
+        for (int s = 0; s < 8; ++s) slots[(uint64_t)s * capacity + i] = b.slots[i * 8 + s];
+        memcpy((uint8_t*)clear + i * 16, &b.clear[i], 16);
+        memcpy((uint8_t*)set + i * 16, &b.set[i], 16);
+    }
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_text_encode(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
+                                 void* words, uint64_t* n_out) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (!text || !n_out) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
+    if (mode != CUBIT_TEXT_ONE && mode != CUBIT_TEXT_PROGRAM) return fail(ctx, CUBIT_ERR_INVALID, "unknown text mode");
+    LoweredBatch b;
+    try {
+        lower_text(ctx, text, base_addr, mode, &b);
+    } catch (const TextError& e) {
+        return fail(ctx, CUBIT_ERR_TEXT, e.what());
+    } catch (const std::exception& e) {
+        return fail(ctx, CUBIT_ERR_INVALID, e.what());
+    }
+    const uint64_t n = b.form.size();
+    *n_out = n;
+    if (n > capacity || !words || n == 0) return CUBIT_OK;
+    std::vector<uint32_t> planes(8 * n);
+    for (uint64_t i = 0; i < n; ++i)
+        for (int s = 0; s < 8; ++s) planes[(uint64_t)s * n + i] = b.slots[i * 8 + s];
+    const int rc = cubit_encode_batch(ctx, b.form.data(), planes.data(), b.ctrl.data(), n, words, CUBIT_MEM_HOST, nullptr);
+    if (rc) return rc;
+    for (uint64_t i = 0; i < n; ++i) {
+        u128 w;
+        memcpy(&w, (uint8_t*)words + i * 16, 16);
+        w = (w & ~b.clear[i]) | b.set[i];
+        memcpy((uint8_t*)words + i * 16, &w, 16);
+    }
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_text_parse(cubit_ctx* ctx, const char* line, uint32_t addr, char* json, uint64_t capacity,
+                                uint64_t* needed) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (!line || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
+    TextInstruction insn;
+    try {
+        insn = parse_cuasm_line(line, addr);
+    } catch (const TextError& e) {
+        return fail(ctx, CUBIT_ERR_TEXT, std::string("parse error: ") + e.what());
+    }
+    static const char* const kKinds[] = {"Reg", "UReg", "Pred", "UPred", "Imm32", "Imm64", "FloatImm", "Addr",
+                                         "ConstMem", "Desc", "BranchTarget", "Barrier", "SysReg", "Label"};
+    std::string j = "{\"key\":";
+    json_escape(insn.key, &j);
+    j += ",\"opcode\":"; json_escape(insn.opcode, &j);
+    j += ",\"opcode_full\":"; json_escape(insn.opcode_full, &j);
+    j += ",\"mod_group\":"; json_escape(extract_mod_group(insn.raw_text), &j);
+    j += ",\"addr\":" + std::to_string(insn.addr);
+    if (insn.has_guard)
+        j += std::string(",\"guard\":{\"pred\":") + std::to_string((int)insn.guard_pred) + ",\"negated\":" +
+             (insn.guard_neg ? "true" : "false") + ",\"uniform\":" + (insn.guard_uniform ? "true" : "false") + "}";
+    else j += ",\"guard\":null";
+    j += ",\"modifiers\":[";
+    for (size_t k = 0; k < insn.modifiers.size(); ++k) { if (k) j += ','; json_escape(insn.modifiers[k], &j); }
+    j += "],\"ctrl\":"; json_escape(format_control_code(insn.ctrl), &j);
+    j += std::string(",\"hand_sched\":") + (insn.hand_sched ? "true" : "false");
+    j += ",\"operands\":[";
+    auto b = [](bool v) { return v ? "true" : "false"; };
+    for (size_t k = 0; k < insn.operands.size(); ++k) {
+        const TextOperand& op = insn.operands[k];
+        if (k) j += ',';
+        j += std::string("{\"type\":\"") + operand_type_label(op) + "\",\"kind\":\"" + kKinds[(size_t)op.kind] + "\"";
+        switch (op.kind) {
+            case OperandKind::Reg:
+                j += ",\"num\":" + std::to_string((int)op.num) + ",\"neg\":" + b(op.neg) + ",\"abs\":" + b(op.abs) +
+                     ",\"inv\":" + b(op.inv) + ",\"reuse\":" + b(op.reuse);
+                break;
+            case OperandKind::UReg:
+                j += ",\"num\":" + std::to_string((int)op.num) + ",\"neg\":" + b(op.neg) + ",\"reuse\":" + b(op.reuse) +
+                     ",\"is_zero\":" + b(op.is_zero);
+                break;
+            case OperandKind::Pred: case OperandKind::UPred:
+                j += ",\"num\":" + std::to_string((int)op.num) + ",\"neg\":" + b(op.neg);
+                break;
+            case OperandKind::Imm32: j += ",\"value\":" + std::to_string((long long)op.imm); break;
+            case OperandKind::Imm64: case OperandKind::FloatImm:
+                j += ",\"bits\":" + std::to_string((unsigned long long)op.bits);
+                break;
+            case OperandKind::Addr: case OperandKind::ConstMem: case OperandKind::Desc:
+                j += std::string(",\"base_reg\":") + (op.has_base ? std::to_string((int)op.base) : "null");
+                if (op.kind != OperandKind::Desc) j += std::string(",\"ur_reg\":") + (op.has_ur ? std::to_string((int)op.ur) : "null");
+                if (op.kind == OperandKind::Desc) j += ",\"ur_idx\":" + std::to_string((int)op.ur_idx);
+                if (op.kind == OperandKind::ConstMem) j += ",\"bank\":" + std::to_string((int)op.bank);
+                if (op.kind != OperandKind::ConstMem) {
+                    j += ",\"base_reg_suffix\":";
+                    if (op.has_suffix) json_escape(op.suffix, &j); else j += "null";
+                }
+                j += ",\"offset\":" + std::to_string((long long)op.offset);
+                break;
+            case OperandKind::BranchTarget: j += ",\"target\":" + std::to_string(op.target); break;
+            case OperandKind::Barrier: j += ",\"num\":" + std::to_string((int)op.num); break;
+            case OperandKind::SysReg: case OperandKind::Label: j += ",\"text\":"; json_escape(op.text, &j); break;
+        }
+        j += '}';
+    }
+    j += "]}";
+    *needed = j.size() + 1;
+    if (json && capacity >= j.size() + 1) memcpy(json, j.c_str(), j.size() + 1);
     return CUBIT_OK;
 }

@@ -42,7 +42,8 @@ typedef enum {
     CUBIT_ERR_NO_DEVICE = -4,  /* compute entry point called on a context without a GPU */
     CUBIT_ERR_ELF = -5,        /* not a little-endian ELF64, or truncated */
     CUBIT_ERR_NOT_FOUND = -6,  /* kernel / variant name not found */
-    CUBIT_ERR_NOMEM = -7
+    CUBIT_ERR_NOMEM = -7,
+    CUBIT_ERR_TEXT = -8        /* SASS text did not parse, or no table entry fits its operands */
 } cubit_status;
 
 enum { CUBIT_MEM_HOST = 0, CUBIT_MEM_DEVICE = 1 };
@@ -214,6 +215,54 @@ int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t
  * loadable module.  Call with out == NULL to get the required size in *out_len. */
 int cubit_elf_build(const char* const* names, const void* const* code, const uint64_t* code_bytes,
                     uint32_t n_kernels, void* out, uint64_t capacity, uint64_t* out_len);
+
+/* ---- SASS text (host) -------------------------------------------------------------------- */
+
+/* Text is handled on the host; only the table-driven part of an encode runs on the GPU.  An
+ * instruction's text is lowered to a record (form, slots, ctrl, as cubit_encode_batch takes)
+ * plus a 128-bit patch: the bits the reference derives from the text itself and not from
+ * table fields (branch targets, register placement fixups, raw-address LDG/STG, the control
+ * word).  The encoded word is (cubit_encode_batch word & ~clear) | set.
+ *
+ * `mode` CUBIT_TEXT_ONE: `text` is one bare instruction, parsed as parse_sass does (reference
+ *   src/parser.rs:358-478); failures set "parse error: ..." / "encode error: ..." as the
+ *   reference's Python encode() raises them (src/python.rs:48-55).
+ * `mode` CUBIT_TEXT_PROGRAM: statements separated by ';' or newlines, optional
+ *   "[B------:R-:W-:-:S01]" control prefixes, "name:" labels resolved to branch targets,
+ *   // and # comments, unparsable lines skipped (parse_multi_sass + resolve_labels, reference
+ *   src/parser.rs:485-588); instruction k sits at base_addr + 16 k.  A "__raw__0x<hex>"
+ *   statement is emitted unchanged (reference src/main.rs:1918-1927).  The reference's
+ *   assemble() additionally runs its scheduling pass over the control codes
+ *   (src/lib.rs:52-54); that pass is not part of this library, control codes are taken as
+ *   written (default B------:R-:W-:-:S01).
+ * Deviation: the reference numbers ".?<n>" opaque modifiers with a counter that is not reset
+ * when the same text is encoded twice in a row (src/encoder.rs:1036-1045); here every
+ * instruction starts at its first value. */
+enum { CUBIT_TEXT_ONE = 0, CUBIT_TEXT_PROGRAM = 1 };
+
+/* Lowers text to records and patches.  Buffers hold `capacity` instructions; slots is
+ * slot-major with stride `capacity` (slot s of instruction i at slots[s * capacity + i]);
+ * clear / set are `capacity` x 16 bytes, little-endian.  *n_out is the instruction count; when
+ * it exceeds capacity (or a buffer is NULL) nothing is written and CUBIT_OK is returned, so a
+ * first call with capacity 0 sizes the buffers.  Works on a context without a GPU. */
+int cubit_text_lower(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
+                     uint16_t* form, uint32_t* slots, uint32_t* ctrl, void* clear, void* set, uint64_t* n_out);
+
+/* Replaces encode(sass, addr) (reference src/python.rs:48-60, CUBIT_TEXT_ONE) and the encode
+ * loop of cubit::assemble (src/lib.rs:49-63, CUBIT_TEXT_PROGRAM): lowers the text, encodes the
+ * records with the batch kernel and applies the patches.  `words` is host memory for
+ * `capacity` x 16 bytes; sizing works as for cubit_text_lower. */
+int cubit_text_encode(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
+                      void* words, uint64_t* n_out);
+
+/* The parsed form of one instruction as JSON, for tools and tests: {"key", "opcode",
+ * "opcode_full", "mod_group", "guard": null | {"pred", "negated", "uniform"}, "modifiers",
+ * "ctrl": "B------:R-:W-:-:S01", "hand_sched", "operands": [{"type": "R", "kind": "Reg", ...}]}.
+ * `line` may carry a control prefix (parse_cuasm_line, reference src/parser.rs:591-604).
+ * *needed is the length including the terminating NUL; nothing is written when it exceeds
+ * capacity. */
+int cubit_text_parse(cubit_ctx* ctx, const char* line, uint32_t addr, char* json, uint64_t capacity,
+                     uint64_t* needed);
 
 #ifdef __cplusplus
 }
