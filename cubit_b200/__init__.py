@@ -5,9 +5,9 @@ Module-level functions carry the names and signatures of the reference's PyO3 mo
 GPU through a process-wide :class:`Codec` created on first use (the reference keeps a
 process-wide table and index the same way, src/python.rs:28-42).  ``encode`` parses the text
 on the host, encodes the record on the GPU and applies the text-derived bits on the host;
-``encode_lines`` does the same for a program with labels.  ``to_sass`` (the printer) and
-``asm`` (which runs the reference's scheduling pass before encoding) are not part of this
-package and raise NotImplementedError.
+``encode_lines`` does the same for a program with labels; ``to_sass`` decodes on the GPU and
+prints on the host.  ``asm`` (which runs the reference's scheduling pass before encoding) is
+not part of this package and raises NotImplementedError.
 """
 from __future__ import annotations
 
@@ -68,7 +68,8 @@ def encode_lines(code: str, addr: int = 0) -> tuple:
 
 
 def to_sass(lo: int, hi: int, addr: int = 0) -> str:
-    raise NotImplementedError("the SASS printer is not part of this package")
+    """SASS text of one 128-bit word, e.g. "IADD3 R5, PT, PT, R9, R4, R5"; encode() reads it back."""
+    return default_codec().to_sass(lo, hi, addr)
 
 
 def asm(code: str, addr: int = 0):

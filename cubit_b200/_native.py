@@ -69,6 +69,9 @@ SIGNATURES = {
                                    C.c_void_p, C.c_void_p, C.c_void_p, u64p]),
     "cubit_text_encode": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_int, C.c_uint64, C.c_void_p, u64p]),
     "cubit_text_parse": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64, u64p]),
+    "cubit_disassemble": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_int, C.c_char_p, C.c_uint64, u64p, u64p]),
+    "cubit_text_print": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_char_p, C.c_uint64, u64p]),
 }
 
 _lib = None

@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB = LIB_DIR / "libcubit_b200.so"
-SOURCES = ["capi.cu", "isa_table.cpp", "flat_table.cpp", "elf_text.cpp", "sass_text.cpp"]
+SOURCES = ["capi.cu", "isa_table.cpp", "flat_table.cpp", "elf_text.cpp", "sass_text.cpp", "sass_print.cpp"]
 HEADERS = ["codec_core.cuh", "flat_table.hpp", "isa_table.hpp", "elf_text.hpp", "sass_text.hpp", "json.hpp",
            "../../include/cubit_b200.h"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

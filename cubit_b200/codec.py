@@ -276,14 +276,19 @@ class Codec:
         """cubit.decode(lo, hi, addr=0): one word through the batch kernel."""
         word = (int(lo) & (2**64 - 1)).to_bytes(8, "little") + (int(hi) & (2**64 - 1)).to_bytes(8, "little")
         form, slots, ctrl, _ = self.decode_batch(np.frombuffer(word, np.uint8))
-        status = (int(ctrl[0]) >> 30) & 3
+        self._raise_if_rejected(lo, hi, int(ctrl[0]))
+        return self.record_to_dict(form[0], slots[:, 0], ctrl[0], addr)
+
+    @staticmethod
+    def _raise_if_rejected(lo: int, hi: int, ctrl: int):
+        """The two decode failures of the reference, with its messages (src/decoder.rs:173, :287)."""
+        status = (ctrl >> 30) & 3
         opcode_bits = int(lo) & 0xFFF
         if status == 1:
             raise ValueError(f"decode error: no instruction matches opcode 0x{opcode_bits:04x}")
         if status == 2:
             clean = (int(lo) & (2**64 - 1)) | ((int(hi) & 0xFFFFFFFF) << 64)
             raise ValueError(f"decode error: no instruction matches code 0x{clean:032x} at opcode 0x{opcode_bits:04x}")
-        return self.record_to_dict(form[0], slots[:, 0], ctrl[0], addr)
 
     # ---- SASS text (host parse, GPU record encode, host patch) ----------------------------
 
@@ -337,6 +342,36 @@ class Codec:
             raise ValueError(self._lib.cubit_last_error(self._ctx).decode())
         self._check(rc)
         return words[:int(n.value)]
+
+    def print_text(self, words, addr: int = 0, records=None) -> list[str]:
+        """SASS text of each 16-byte word (uint8[n, 16]); word i is taken to sit at addr + 16 i.
+        `records` = (form, slots, ctrl) of the words skips the decode (and then needs no GPU).
+        Words that match no variant print as the disassembler's "/* ? 0x... */" comment."""
+        words = np.ascontiguousarray(words, np.uint8).reshape(-1, 16)
+        n = len(words)
+        if n == 0:
+            return []
+        if records is None:
+            form, slots, ctrl, _ = self.decode_batch(words)
+        else:
+            form, slots, ctrl = records
+        form = np.ascontiguousarray(form, np.uint16); slots = np.ascontiguousarray(slots, np.uint32)
+        ctrl = np.ascontiguousarray(ctrl, np.uint32)
+        need = C.c_uint64()
+        self._check(self._lib.cubit_text_print(self._ctx, _ptr(words), n, addr, _ptr(form), _ptr(slots), _ptr(ctrl),
+                                               None, 0, need))
+        buf = C.create_string_buffer(need.value)
+        self._check(self._lib.cubit_text_print(self._ctx, _ptr(words), n, addr, _ptr(form), _ptr(slots), _ptr(ctrl),
+                                               buf, need.value, need))
+        return buf.value.decode().split("\n")[:n]
+
+    def to_sass(self, lo: int, hi: int, addr: int = 0) -> str:
+        """cubit.to_sass(lo, hi, addr=0) (reference src/python.rs:186-197)."""
+        word = (int(lo) & (2**64 - 1)).to_bytes(8, "little") + (int(hi) & (2**64 - 1)).to_bytes(8, "little")
+        words = np.frombuffer(word, np.uint8).reshape(1, 16)
+        form, slots, ctrl, _ = self.decode_batch(words)
+        self._raise_if_rejected(lo, hi, int(ctrl[0]))
+        return self.print_text(words, addr, (form, slots, ctrl))[0]
 
     def encode(self, sass: str, addr: int = 0) -> tuple[int, int]:
         """cubit.encode(sass, addr=0) -> (lo, hi) (reference src/python.rs:48-60)."""
@@ -416,6 +451,28 @@ class Codec:
                     for i in range(k)]
         finally:
             self._lib.cubit_elf_free(elf)
+
+    def disassemble(self, data: bytes, kernel: str | None = None, frozen: bool = False, want_raw_count: bool = False):
+        """Listing of a cubin image in the reference's `disassemble` formats (src/main.rs:401-627):
+        plain (address comments and "@sched" annotations) or, with `frozen`, a re-assemblable
+        .entry block with labels and control-code prefixes in which every line that would not
+        encode back to its word is written as __raw__0x...  Returns the text (and the number of
+        raw / undecodable lines with `want_raw_count`)."""
+        buf = np.frombuffer(data, np.uint8)
+        elf = C.c_void_p()
+        rc = self._lib.cubit_elf_parse(_ptr(buf), len(buf), C.byref(elf))
+        if rc:
+            raise OSError("load error: " + self._lib.cubit_last_error(None).decode())
+        try:
+            need, n_raw = C.c_uint64(), C.c_uint64()
+            only = kernel.encode() if kernel is not None else None
+            self._check(self._lib.cubit_disassemble(self._ctx, elf, only, int(frozen), None, 0, need, n_raw))
+            out = C.create_string_buffer(need.value)
+            self._check(self._lib.cubit_disassemble(self._ctx, elf, only, int(frozen), out, need.value, need, n_raw))
+        finally:
+            self._lib.cubit_elf_free(elf)
+        text = out.value.decode()
+        return (text, int(n_raw.value)) if want_raw_count else text
 
     def decode_kernel(self, cubin_path: str | os.PathLike, kernel_name: str) -> list[dict]:
         """cubit.decode_kernel(cubin_path, kernel_name) (reference src/python.rs:104-169)."""

@@ -21,7 +21,7 @@ static void wr64(uint8_t* p, uint64_t v) { for (int i = 0; i < 8; ++i) p[i] = ui
 
 static const uint32_t SHT_PROGBITS = 1, SHT_SYMTAB = 2, SHT_STRTAB = 3, SHT_NOTE = 7, SHT_NOBITS = 8;
 
-std::vector<TextSection> elf_text_sections(const uint8_t* b, uint64_t len) {
+std::vector<ElfSection> elf_sections(const uint8_t* b, uint64_t len) {
     if (len < 64 || memcmp(b, "\x7f" "ELF", 4) != 0) throw std::runtime_error("failed to parse ELF: bad magic");
     if (b[4] != 2) throw std::runtime_error("failed to parse ELF: not a 64-bit ELF");
     if (b[5] != 1) throw std::runtime_error("failed to parse ELF: not little-endian");
@@ -29,7 +29,7 @@ std::vector<TextSection> elf_text_sections(const uint8_t* b, uint64_t len) {
     const uint16_t shentsize = rd16(b + 0x3A);
     uint64_t shnum = rd16(b + 0x3C);
     uint32_t shstrndx = rd16(b + 0x3E);
-    std::vector<TextSection> out;
+    std::vector<ElfSection> out;
     if (shoff == 0) return out;
     if (shentsize != 64) throw std::runtime_error("failed to parse ELF: unexpected section header size");
     if (shoff > len || len - shoff < 64) throw std::runtime_error("failed to parse ELF: section table past end of file");
@@ -49,10 +49,16 @@ std::vector<TextSection> elf_text_sections(const uint8_t* b, uint64_t len) {
         const char* name = (const char*)b + str_off + name_off;
         const void* nul = memchr(name, 0, size_t(str_size - name_off));
         if (!nul) continue;
-        const std::string nm(name, (const char*)nul - name);
-        const bool is_text = nm == ".text" || nm.compare(0, 6, ".text.") == 0;
-        if (is_text && rd32(sh + 4) == SHT_PROGBITS && rd64(sh + 0x20) > 0)
-            out.push_back(TextSection{nm, rd64(sh + 0x18), rd64(sh + 0x20)});
+        out.push_back(ElfSection{std::string(name, (const char*)nul - name), rd32(sh + 4), rd64(sh + 0x18), rd64(sh + 0x20)});
+    }
+    return out;
+}
+
+std::vector<TextSection> elf_text_sections(const uint8_t* b, uint64_t len) {
+    std::vector<TextSection> out;
+    for (const ElfSection& s : elf_sections(b, len)) {
+        const bool is_text = s.name == ".text" || s.name.compare(0, 6, ".text.") == 0;
+        if (is_text && s.type == SHT_PROGBITS && s.size > 0) out.push_back(TextSection{s.name, s.offset, s.size});
     }
     return out;
 }

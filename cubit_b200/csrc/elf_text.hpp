@@ -14,6 +14,14 @@ struct TextSection {
 // Throws std::runtime_error for anything that is not a well-formed little-endian ELF64.
 std::vector<TextSection> elf_text_sections(const uint8_t* bytes, uint64_t len);
 
+struct ElfSection {
+    std::string name;
+    uint32_t type;
+    uint64_t offset, size;   // sh_offset, sh_size
+};
+// Every section with a readable name, in section-header order; same errors as above.
+std::vector<ElfSection> elf_sections(const uint8_t* bytes, uint64_t len);
+
 struct BuildKernel {
     std::string name;
     const uint8_t* code;

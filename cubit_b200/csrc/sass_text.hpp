@@ -92,6 +92,23 @@ struct LoweredInstruction {
     u128 clear = 0, set = 0;
 };
 
+// A decoded instruction as the printer reads it (reference src/decoder.rs:15-59): table fields
+// with their decoded values in table order, then the synthesized neg / abs fields.
+struct PrintField {
+    uint32_t shift = 0, bits = 0;
+    uint64_t value = 0;
+    int32_t token_idx = 0;
+    std::string ext;      // extraction name as the decoder reports it (reference src/decoder.rs:679-705)
+};
+struct DecodedView {
+    std::string key, mod_group, opcode;
+    std::vector<PrintField> fields;
+    u128 raw = 0;
+    uint32_t addr = 0;
+};
+// SASS text without the trailing " ;" (reference src/printer.rs:12-212).
+std::string to_sass(const DecodedView& insn);
+
 class TextEncoder {
 public:
     explicit TextEncoder(const IsaTable& table);

@@ -264,6 +264,35 @@ int cubit_text_encode(cubit_ctx* ctx, const char* text, uint32_t base_addr, int 
 int cubit_text_parse(cubit_ctx* ctx, const char* line, uint32_t addr, char* json, uint64_t capacity,
                      uint64_t* needed);
 
+/* Replaces printer::to_sass (reference src/printer.rs:12) and to_sass(lo, hi, addr) (src/python.rs:186-197)
+ * for a batch: prints word i, located at base_addr + 16 i (branch targets are absolute), as one
+ * line of SASS text without the trailing " ;", each line ended by '\n'.  form / slots / ctrl
+ * are the records of the words as cubit_decode_batch wrote them (slots slot-major, stride n);
+ * pass all three NULL to have the words decoded here (needs a GPU).  A word that matches no
+ * variant prints as the disassembler's placeholder comment with the word in hex (reference
+ * src/main.rs:497).  All buffers are host memory.  *needed is the text length including the
+ * terminating NUL; nothing is written when it exceeds capacity. */
+int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, uint32_t base_addr, const uint16_t* form,
+                     const uint32_t* slots, const uint32_t* ctrl, char* out, uint64_t capacity, uint64_t* needed);
+
+/* Replaces cmd_disassemble (reference src/main.rs:401-627): a listing of every text section of
+ * the cubin (or only the kernel whose name, without the ".text." prefix, equals only_kernel).
+ * All words are decoded in one launch per device and printed on the host.
+ *   frozen == 0: "// <kernel>", an optional "    .shared smem[N]", then one line per word,
+ *     "  / *addr* /  <text> / * @sched 0x<5 hex> * / ;" (written without the spaces inside the
+ *     comment marks), or the placeholder comment for a word that matches no variant.
+ *   frozen != 0: a re-assemblable ".entry" block: ".reg", ".param" and ".shared" lines from the
+ *     kernel's .nv.info / .nv.shared sections, "L_<addr>:" labels on branch targets, every
+ *     instruction prefixed with its control code "[B------:R-:W-:-:S01]".  Each printed line is
+ *     checked the way the reference does: its text is parsed and encoded again (one batch on
+ *     the GPU) and must equal the original word outside the scheduling field; lines that fail,
+ *     and words that match no variant, are emitted as "__raw__0x<32 hex> ;".  *n_raw (optional)
+ *     counts those lines.
+ * *needed is the text length including the terminating NUL; nothing is written when it
+ * exceeds capacity. */
+int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const char* only_kernel, int frozen, char* out,
+                      uint64_t capacity, uint64_t* needed, uint64_t* n_raw);
+
 #ifdef __cplusplus
 }
 #endif
