@@ -15,10 +15,10 @@ import os
 import threading
 
 from .codec import (FORM_NONE, MEM_DEVICE, MEM_HOST, MIX_FAMILY, MIX_UNIFORM, MIX_ZIPF, RT_EXACT, RT_MISMATCH,
-                    RT_REJECTED, SCHED_MASK, Codec, CubitError, FieldMeta, VariantMeta, build_cubin, unpack_ctrl)
+                    RT_REJECTED, SCHED_MASK, Codec, CubitError, FieldMeta, VariantMeta, build_cubin, patch_text, unpack_ctrl)
 from .sharding import shard_range, shard_sections
 
-__all__ = ["Codec", "CubitError", "FieldMeta", "VariantMeta", "build_cubin", "unpack_ctrl", "shard_range",
+__all__ = ["Codec", "CubitError", "FieldMeta", "VariantMeta", "build_cubin", "patch_text", "unpack_ctrl", "shard_range",
            "shard_sections", "decode", "decode_kernel", "table_info", "encode", "encode_lines", "to_sass", "asm", "FORM_NONE",
            "MEM_HOST", "MEM_DEVICE", "MIX_UNIFORM", "MIX_ZIPF", "MIX_FAMILY", "RT_EXACT", "RT_MISMATCH", "RT_REJECTED",
            "SCHED_MASK"]

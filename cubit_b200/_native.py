@@ -22,6 +22,11 @@ class FieldInfo(C.Structure):
                 ("stored_bits", C.c_uint32), ("name", C.c_char_p), ("extraction", C.c_char_p)]
 
 
+class PatchStats(C.Structure):
+    _fields_ = [("n_words", C.c_uint64), ("n_reencoded", C.c_uint64), ("n_kept", C.c_uint64), ("n_changed", C.c_uint64),
+                ("n_unfaithful", C.c_uint64)]
+
+
 class KernelMeta(C.Structure):
     _fields_ = [("regcount", C.c_uint32), ("num_barriers", C.c_uint32), ("max_reg", C.c_uint32),
                 ("barrier_mask", C.c_uint32), ("first_exit", C.c_uint64), ("n_exits", C.c_uint64)]
@@ -69,6 +74,8 @@ SIGNATURES = {
                                    C.c_void_p, C.c_void_p, C.c_void_p, u64p]),
     "cubit_text_encode": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_int, C.c_uint64, C.c_void_p, u64p]),
     "cubit_text_parse": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64, u64p]),
+    "cubit_patch_elf": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, u64p, C.POINTER(PatchStats)]),
+    "cubit_elf_patch_text": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
     "cubit_disassemble": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_int, C.c_char_p, C.c_uint64, u64p, u64p]),
     "cubit_text_print": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_char_p, C.c_uint64, u64p]),

@@ -474,6 +474,24 @@ class Codec:
         text = out.value.decode()
         return (text, int(n_raw.value)) if want_raw_count else text
 
+    def patch(self, data: bytes) -> tuple[bytes, dict]:
+        """The reference's `patch` over a cubin image (src/main.rs:691-764): every instruction goes
+        decode -> print -> parse -> encode and, where that works, gets its low 64 bits rewritten
+        (high 64 bits are kept).  Returns (new image, counters)."""
+        buf = np.frombuffer(data, np.uint8)
+        elf = C.c_void_p()
+        rc = self._lib.cubit_elf_parse(_ptr(buf), len(buf), C.byref(elf))
+        if rc:
+            raise OSError("load error: " + self._lib.cubit_last_error(None).decode())
+        try:
+            out = np.empty(len(buf), np.uint8)
+            need = C.c_uint64()
+            stats = _native.PatchStats()
+            self._check(self._lib.cubit_patch_elf(self._ctx, elf, _ptr(out), len(out), need, C.byref(stats)))
+        finally:
+            self._lib.cubit_elf_free(elf)
+        return out.tobytes(), {name: int(getattr(stats, name)) for name, _ in stats._fields_}
+
     def decode_kernel(self, cubin_path: str | os.PathLike, kernel_name: str) -> list[dict]:
         """cubit.decode_kernel(cubin_path, kernel_name) (reference src/python.rs:104-169)."""
         try:
@@ -510,4 +528,28 @@ def build_cubin(kernels: Sequence[tuple[str, bytes]]) -> bytes:
     rc = lib.cubit_elf_build(names, codes, sizes, n, _ptr(out), need.value, C.byref(need))
     if rc:
         raise CubitError(rc, lib.cubit_last_error(None).decode())
+    return out.tobytes()
+
+
+def patch_text(data: bytes, index: int, code: bytes) -> bytes:
+    """The cubin image with text section `index` replaced by `code`; a different length moves every
+    offset behind it (reference CubinFile::patch_text, src/elf.rs:71-219)."""
+    lib = _native.load_library()
+    buf = np.frombuffer(data, np.uint8)
+    elf = C.c_void_p()
+    rc = lib.cubit_elf_parse(_ptr(buf), len(buf), C.byref(elf))
+    if rc:
+        raise OSError("load error: " + lib.cubit_last_error(None).decode())
+    try:
+        new = np.frombuffer(code, np.uint8)
+        need = C.c_uint64()
+        rc = lib.cubit_elf_patch_text(elf, index, _ptr(new) if len(new) else None, len(new), None, 0, need)
+        if rc:
+            raise CubitError(rc, lib.cubit_last_error(None).decode())
+        out = np.empty(need.value, np.uint8)
+        rc = lib.cubit_elf_patch_text(elf, index, _ptr(new) if len(new) else None, len(new), _ptr(out), len(out), need)
+        if rc:
+            raise CubitError(rc, lib.cubit_last_error(None).decode())
+    finally:
+        lib.cubit_elf_free(elf)
     return out.tobytes()

@@ -1623,3 +1623,91 @@ extern "C" int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const cha
     if (out && capacity >= listing.size() + 1) memcpy(out, listing.c_str(), listing.size() + 1);
     return CUBIT_OK;
 }
+
+// ---- cubin rewriting -------------------------------------------------------------------------
+
+extern "C" int cubit_patch_elf(cubit_ctx* ctx, const cubit_elf* elf, void* out, uint64_t capacity, uint64_t* needed,
+                               cubit_patch_stats* stats) {
+    if (!ctx) return CUBIT_ERR_INVALID;
+    if (!elf || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
+    cubit_patch_stats st;
+    memset(&st, 0, sizeof st);
+    const uint32_t n_sec = (uint32_t)elf->text.size();
+    std::vector<uint64_t> start(n_sec + 1, 0);
+    int rc = cubit_decode_elf(ctx, elf, nullptr, n_sec, start.data(), 0, nullptr, nullptr, nullptr, nullptr, nullptr);
+    if (rc) return rc;
+    const uint64_t total = start.back();
+    st.n_words = total;
+    *needed = elf->len;
+    if (!out || capacity < elf->len) { if (stats) *stats = st; return CUBIT_OK; }
+    std::vector<uint16_t> form(total);
+    std::vector<uint32_t> slots(8 * total), ctrl(total);
+    std::vector<uint8_t> words(16 * total);
+    if (total) {
+        rc = cubit_decode_elf(ctx, elf, nullptr, n_sec, start.data(), total, form.data(), slots.data(), ctrl.data(),
+                              words.data(), nullptr);
+        if (rc) return rc;
+    }
+    // decode -> print -> parse -> lower on the host; what lowers is encoded in one batch.
+    LoweredBatch b;
+    std::vector<uint64_t> where;
+    for (uint32_t k = 0; k < n_sec; ++k)
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) {
+            if (form[i] == 0xFFFFu) continue;
+            const uint32_t addr = (uint32_t)((i - start[k]) * 16);
+            try {
+                const std::string text = print_word(ctx, words.data(), i, total, addr, form.data(), slots.data(), ctrl.data());
+                LoweredBatch one;
+                lower_text(ctx, text.c_str(), addr, CUBIT_TEXT_ONE, &one);
+                b.form.push_back(one.form[0]); b.ctrl.push_back(one.ctrl[0]);
+                b.slots.insert(b.slots.end(), one.slots.begin(), one.slots.end());
+                b.clear.push_back(one.clear[0]); b.set.push_back(one.set[0]);
+                where.push_back(i);
+            } catch (const std::exception&) {
+                // kept as it is
+            }
+        }
+    const uint64_t m = where.size();
+    std::vector<uint8_t> enc(16 * m);
+    if (m) {
+        std::vector<uint32_t> planes(8 * m);
+        for (uint64_t i = 0; i < m; ++i)
+            for (int s = 0; s < 8; ++s) planes[(uint64_t)s * m + i] = b.slots[i * 8 + s];
+        rc = cubit_encode_batch(ctx, b.form.data(), planes.data(), b.ctrl.data(), m, enc.data(), CUBIT_MEM_HOST, nullptr);
+        if (rc) return rc;
+    }
+    memcpy(out, elf->bytes, elf->len);
+    uint8_t* file = (uint8_t*)out;
+    const u128 keep = ~((u128)0x1FFFF << 105);
+    std::vector<uint64_t> file_off(total);
+    for (uint32_t k = 0; k < n_sec; ++k)
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) file_off[i] = elf->text[k].offset + (i - start[k]) * 16;
+    for (uint64_t j = 0; j < m; ++j) {
+        u128 e, w;
+        memcpy(&e, enc.data() + j * 16, 16);
+        memcpy(&w, words.data() + where[j] * 16, 16);
+        e = (e & ~b.clear[j]) | b.set[j];
+        if (((e ^ w) & keep) != 0) ++st.n_unfaithful;
+        if ((uint64_t)e != (uint64_t)w) ++st.n_changed;
+        const uint64_t lo = (uint64_t)e;
+        memcpy(file + file_off[where[j]], &lo, 8);   // the high half stays the original's
+    }
+    st.n_reencoded = m;
+    st.n_kept = total - m;
+    if (stats) *stats = st;
+    return CUBIT_OK;
+}
+
+extern "C" int cubit_elf_patch_text(const cubit_elf* elf, uint32_t index, const void* code, uint64_t code_len, void* out,
+                                    uint64_t capacity, uint64_t* needed) {
+    if (!elf || !needed || (code_len && !code)) return fail(nullptr, CUBIT_ERR_INVALID, "null argument");
+    std::vector<uint8_t> file;
+    try {
+        file = elf_patch_text(elf->bytes, elf->len, index, (const uint8_t*)code, code_len);
+    } catch (const std::exception& e) {
+        return fail(nullptr, CUBIT_ERR_ELF, e.what());
+    }
+    *needed = file.size();
+    if (out && capacity >= file.size()) memcpy(out, file.data(), file.size());
+    return CUBIT_OK;
+}

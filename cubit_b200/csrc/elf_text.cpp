@@ -63,6 +63,82 @@ std::vector<TextSection> elf_text_sections(const uint8_t* b, uint64_t len) {
     return out;
 }
 
+// ---- text replacement ----------------------------------------------------------------------
+
+std::vector<uint8_t> elf_patch_text(const uint8_t* bytes, uint64_t len, uint32_t index, const uint8_t* code,
+                                    uint64_t code_len) {
+    const std::vector<TextSection> text = elf_text_sections(bytes, len);
+    if (index >= text.size()) throw std::runtime_error("text section index out of range");
+    const uint64_t start = text[index].offset, old_size = text[index].size;
+    if (start > len || old_size > len - start)
+        throw std::runtime_error("text section " + text[index].name + " extends past end of file");
+    std::vector<uint8_t> out;
+    out.reserve(len - old_size + code_len);
+    out.insert(out.end(), bytes, bytes + start);
+    out.insert(out.end(), code, code + code_len);
+    out.insert(out.end(), bytes + start + old_size, bytes + len);
+    if (code_len == old_size) return out;
+
+    const int64_t delta = (int64_t)code_len - (int64_t)old_size;
+    uint8_t* b = out.data();
+    const uint64_t n = out.size();
+    auto moved = [&](uint64_t v) { return (uint64_t)((int64_t)v + delta); };
+    if (rd64(b + 0x28) > start) wr64(b + 0x28, moved(rd64(b + 0x28)));
+    if (rd64(b + 0x20) > start) wr64(b + 0x20, moved(rd64(b + 0x20)));
+    const uint64_t shoff = rd64(b + 0x28), shnum = rd16(b + 0x3C), phoff = rd64(b + 0x20), phnum = rd16(b + 0x38);
+    for (uint64_t p = 0; p < phnum; ++p) {
+        const uint64_t ph = phoff + p * 56;
+        if (ph + 56 > n) break;
+        const uint64_t p_offset = rd64(b + ph + 8), p_filesz = rd64(b + ph + 0x20);
+        if (p_offset <= start && start < p_offset + p_filesz) {
+            wr64(b + ph + 0x20, moved(p_filesz));
+            wr64(b + ph + 0x28, moved(rd64(b + ph + 0x28)));
+        } else if (p_offset > start) {
+            wr64(b + ph + 8, moved(p_offset));
+        }
+    }
+    int64_t text_shndx = -1;
+    for (uint64_t s = 0; s < shnum; ++s) {
+        const uint64_t sh = shoff + s * 64;
+        if (sh + 64 > n) break;
+        const uint64_t sh_offset = rd64(b + sh + 0x18), sh_size = rd64(b + sh + 0x20);
+        if (sh_offset == start && sh_size == old_size) { wr64(b + sh + 0x20, code_len); text_shndx = (int64_t)s; }
+        else if (sh_offset > start) wr64(b + sh + 0x18, moved(sh_offset));
+    }
+    if (text_shndx >= 0)
+        for (uint64_t s = 0; s < shnum; ++s) {
+            const uint64_t sh = shoff + s * 64;
+            if (sh + 64 > n) break;
+            if (rd32(b + sh + 4) != SHT_SYMTAB) continue;
+            const uint64_t sym_off = rd64(b + sh + 0x18), sym_total = rd64(b + sh + 0x20);
+            for (uint64_t i = 0; i < sym_total / 24; ++i) {
+                const uint64_t so = sym_off + i * 24;
+                if (so + 24 > n) break;
+                if (rd16(b + so + 6) == (uint64_t)text_shndx && (b[so + 4] >> 4) >= 1) wr64(b + so + 16, code_len);
+            }
+            break;   // the first symbol table only
+        }
+    // The first section that starts with a DWARF64 length marker is taken to be .debug_frame.
+    for (uint64_t s = 0; s < shnum; ++s) {
+        const uint64_t sh = shoff + s * 64;
+        if (sh + 64 > n) break;
+        const uint64_t sh_offset = rd64(b + sh + 0x18), sh_size = rd64(b + sh + 0x20);
+        if (sh_size < 48 || sh_offset > n || sh_size > n - sh_offset) continue;
+        if (rd32(b + sh_offset) != 0xFFFFFFFFu) continue;
+        uint64_t pos = sh_offset;
+        const uint64_t end = sh_offset + sh_size;
+        while (pos + 36 <= end) {
+            if (rd32(b + pos) != 0xFFFFFFFFu) break;
+            const uint64_t length = rd64(b + pos + 4);
+            if (rd64(b + pos + 12) != ~0ull && rd64(b + pos + 28) == old_size) wr64(b + pos + 28, code_len);
+            if (length > end - pos) break;
+            pos += 12 + length;
+        }
+        break;
+    }
+    return out;
+}
+
 // ---- builder -----------------------------------------------------------------------------
 
 namespace {

@@ -293,6 +293,33 @@ int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, uint32_t bas
 int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const char* only_kernel, int frozen, char* out,
                       uint64_t capacity, uint64_t* needed, uint64_t* n_raw);
 
+/* ---- cubin rewriting ----------------------------------------------------------------------- */
+
+typedef struct {
+    uint64_t n_words;      /* instruction words in the chosen text sections */
+    uint64_t n_reencoded;  /* words whose printed text parsed and encoded: their low 64 bits were rewritten */
+    uint64_t n_kept;       /* words left as they were: no variant matches, or the text does not encode */
+    uint64_t n_changed;    /* re-encoded words whose low 64 bits differ from the original */
+    uint64_t n_unfaithful; /* re-encoded words that differ from the original outside the scheduling field */
+} cubit_patch_stats;
+
+/* Replaces cmd_patch (reference src/main.rs:691-764): every word of every text section goes
+ * decode -> print -> parse -> encode; where that succeeds the word's low 64 bits are replaced by
+ * the re-encoded ones and its high 64 bits are kept (src/main.rs:740-746), otherwise the word is
+ * kept.  Here: one decode launch per device over all sections, printing and lowering on the
+ * host, one encode launch.  `out` receives the whole file (same length as the input);
+ * *needed is that length, nothing is written when it exceeds capacity. */
+int cubit_patch_elf(cubit_ctx* ctx, const cubit_elf* elf, void* out, uint64_t capacity, uint64_t* needed,
+                    cubit_patch_stats* stats);
+
+/* Replaces CubinFile::patch_text (reference src/elf.rs:71-219): the file with text section
+ * `index` (as numbered by cubit_elf_text) replaced by `code`.  A different length splices the
+ * file and moves every offset behind the section (section and program headers, e_shoff / e_phoff,
+ * sizes of the section's symbols, a DWARF64 .debug_frame range equal to the old size).
+ * *needed is the new file length; nothing is written when it exceeds capacity. */
+int cubit_elf_patch_text(const cubit_elf* elf, uint32_t index, const void* code, uint64_t code_len, void* out,
+                         uint64_t capacity, uint64_t* needed);
+
 #ifdef __cplusplus
 }
 #endif
