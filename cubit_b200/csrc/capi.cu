@@ -107,8 +107,8 @@ template <class HOT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
 encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
               uint64_t slot_stride, const uint32_t* __restrict__ ctrl, uint64_t n, uint4* __restrict__ words) {
-    // The encode kernel stages its own window: extraction and variant records.
-    const FlatView t = stage_table<HOT>(tg, tg.at.ext[0], tg.at.enc_end);
+    // The encode kernel stages its own window: deposit and variant records.
+    const FlatView t = stage_table<HOT>(tg, tg.at.enc, tg.at.enc_end);
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
         uint32_t s[8];
@@ -601,7 +601,7 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         if (rc) return rc;
         d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
         d->hot_bytes = ft.at.hot_words * 4;
-        d->enc_bytes = (ft.at.enc_end - ft.at.ext[0]) * 4;
+        d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
         int optin = 0;
         CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
         d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;

@@ -707,6 +707,42 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         if (unique.size() / XR_WORDS > 0xFFFF) throw std::runtime_error("too many distinct field layouts");
         ft.ext.swap(unique);
     }
+    // The encoder's deposit records, one per extraction record and derived from it alone.
+    {
+        const size_t n_ext = ft.ext.size() / XR_WORDS;
+        ft.enc.assign(n_ext * ER_WORDS, 0);
+        for (size_t r = 0; r < n_ext; ++r) {
+            const uint32_t* xr = &ft.ext[r * XR_WORDS];
+            uint32_t* er = &ft.enc[r * ER_WORDS];
+            const uint32_t cfg = xr[XR_CFG];
+            uint32_t amount[8] = {0, 0, 0, 0, 0, 0, 0, 0}, amount7[3] = {0, 0, 0};
+            if ((cfg >> XC_LAYOUT_POS) & 1u) {
+                for (uint32_t k = 0; k < 3; ++k) er[ER_MASK + 3 * k + k] = xr[XR_MASK + k];   // slot k is limb k, in place
+            } else {
+                for (uint32_t s = 0; s < 8; ++s) {
+                    const uint32_t d = (xr[XR_DESC + (s >> 1)] >> (16 * (s & 1))) & 0xFFFFu;
+                    const uint32_t src = d & 127u, take = d >> 7;
+                    if (!take) continue;
+                    const uint32_t w = src >> 5, sh = src & 31u;
+                    const uint32_t ones = take >= 32 ? 0xFFFFFFFFu : ((1u << take) - 1u);
+                    const uint32_t lo = ones << sh, hi = sh ? ones >> (32u - sh) : 0u;
+                    if (w > 2 || (hi && w + 1 > 2)) throw std::runtime_error("stored field bits above bit 95");
+                    er[ER_MASK + 3 * s + w] |= lo;
+                    if (hi) er[ER_MASK + 3 * s + w + 1] |= hi;
+                    amount[s] = sh;
+                    if (s == 7) amount7[0] = amount7[1] = amount7[2] = sh;
+                }
+                if (xr[XR_MASK] | xr[XR_MASK + 1] | xr[XR_MASK + 2]) {   // slot 7 holds the 1-bit fields of all limbs
+                    for (uint32_t k = 0; k < 3; ++k) er[ER_MASK + 21 + k] = xr[XR_MASK + k];
+                    amount7[0] = 0;
+                    amount7[1] = (32u - (cfg & 31u)) & 31u;
+                    amount7[2] = (32u - ((cfg >> 5) & 31u)) & 31u;
+                }
+            }
+            for (uint32_t s = 0; s < 6; ++s) er[ER_ROT_A] |= amount[s] << (5 * s);
+            er[ER_ROT_B] = amount[6] | (amount7[0] << 5) | (amount7[1] << 10) | (amount7[2] << 15);
+        }
+    }
 
     // Buckets on and_base bits 11:0, then the split tree inside each bucket.  Variants that
     // can never match (constant ones above bit 95) still make their opcode bits "known".
@@ -752,6 +788,11 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     for (size_t q = 0; q < 2; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
+    L.enc_stride = uint32_t(ft.enc.size() / ER_WORDS * 4);
+    for (size_t q = 0; q < ER_WORDS / 4; ++q) {
+        const uint32_t at = place(quad_plane(ft.enc, ER_WORDS, q));
+        if (q == 0) L.enc = at;
+    }
     for (size_t q = 0; q < 2; ++q) L.var[q] = place(quad_plane(ft.var, VR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.enc_end = uint32_t(ft.blob.size());

@@ -38,7 +38,8 @@ struct FlatTable {
     std::vector<uint32_t> classes;   // CR_WORDS each
     std::vector<uint32_t> flagbest;  // FB_WORDS per class that has several members
     std::vector<uint32_t> broad;     // BR_WORDS each
-    std::vector<uint32_t> ext;       // XR_WORDS per variant
+    std::vector<uint32_t> ext;       // XR_WORDS per distinct field layout
+    std::vector<uint32_t> enc;       // ER_WORDS per distinct field layout: the encoder's view of `ext`
     std::vector<uint32_t> var;       // VR_WORDS per variant
     std::vector<uint32_t> gfields;
     std::vector<uint32_t> metaf;     // MF_WORDS per variant

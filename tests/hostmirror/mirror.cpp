@@ -65,7 +65,7 @@ void mir_info(void* h, uint32_t* out) {
 void mir_blob(void* h, const uint32_t** blob, uint32_t* layout24) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 24 * sizeof(uint32_t), "layout size");
+    static_assert(sizeof(BlobLayout) == 26 * sizeof(uint32_t), "layout size");
     memcpy(layout24, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
