@@ -103,6 +103,8 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t
     }
 }
 
+constexpr int kEncodeUnroll = 2;   // measured: 1 -> 78.9, 2 -> 84.4, 3 -> 80.9 Ginsn/s (64 registers at 3)
+
 template <class HOT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
 encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
@@ -110,13 +112,28 @@ encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __
     // The encode kernel stages its own window: deposit and variant records.
     const FlatView t = stage_table<HOT>(tg, tg.at.enc, tg.at.enc_end);
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
-        uint32_t s[8];
+    // kEncodeUnroll records per thread and trip: all their loads are in flight before the first is used.
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += kEncodeUnroll * step) {
+        uint32_t sl[kEncodeUnroll][8], f[kEncodeUnroll], c[kEncodeUnroll];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) s[k] = __ldcs(slots + (uint64_t)k * slot_stride + i);
-        uint4 w;
-        encode_record<HOT, HOT>(t, __ldcs(form + i), s, __ldcs(ctrl + i), &w.x, &w.y, &w.z, &w.w);
-        __stcs(words + i, w);
+        for (int u = 0; u < kEncodeUnroll; ++u) {
+            const uint64_t j = i + (uint64_t)u * step;
+            f[u] = FORM_NONE; c[u] = 0;
+            if (j < n) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) sl[u][k] = __ldcs(slots + (uint64_t)k * slot_stride + j);
+                f[u] = __ldcs(form + j); c[u] = __ldcs(ctrl + j);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kEncodeUnroll; ++u) {
+            const uint64_t j = i + (uint64_t)u * step;
+            if (j < n) {
+                uint4 w;
+                encode_record<HOT, HOT>(t, f[u], sl[u], c[u], &w.x, &w.y, &w.z, &w.w);
+                __stcs(words + j, w);
+            }
+        }
     }
 }
 

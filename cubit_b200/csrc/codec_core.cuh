@@ -153,7 +153,8 @@ enum {                      // variant record (encode side), 8 u32, cold
     VR_EPOCH = 3,           // epoch upper32 of the key (0x000fc200 when the table has none)
     VR_FLAGS = 4,
     VR_GFIELDS = 5,         // gfield_start | gfield_count << 24
-    VR_EXT = 6,             // index of the variant's extraction record
+    VR_EXT = 6,             // [15:0] index of the variant's extraction record; [21:16] which of the six mask
+                            // quads of its deposit record hold anything (the encoder skips the others)
     VR_WORDS = 8,
 };
 enum : uint32_t {
@@ -606,9 +607,11 @@ CB_HD void encode_record(const FlatView& t, uint32_t form, const uint32_t slots[
     uint32_t code0 = va.x, code1 = va.y, code2 = va.z;
     // Two slots per pair of mask quads: {s0k0 s0k1 s0k2 s1k0} {s1k1 s1k2 ...}.
     uint32_t m[24];
+    const uint32_t need = vb.z >> 16;
 #pragma unroll
     for (int k = 0; k < 6; ++k) {
-        const Quad q = ENC::q(t, x + (uint32_t)k * t.at.enc_stride);
+        Quad q = {0u, 0u, 0u, 0u};
+        if ((need >> k) & 1u) q = ENC::q(t, x + (uint32_t)k * t.at.enc_stride);
         m[4 * k] = q.x; m[4 * k + 1] = q.y; m[4 * k + 2] = q.z; m[4 * k + 3] = q.w;
     }
 #pragma unroll
