@@ -15,6 +15,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <exception>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -268,6 +269,7 @@ struct cubit_ctx {
     std::map<std::thread::id, std::string> errors;
     std::mutex synth_mu;
     std::unique_ptr<TextEncoder> text;   // built with the context; reads `table`
+    std::vector<VariantPrintCache> print_cache;   // per variant, for the printer
 };
 
 struct cubit_elf {
@@ -600,6 +602,7 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
     }
     const FlatTable& ft = ctx->flat;
     ctx->text.reset(new TextEncoder(ctx->table));
+    for (const VariantMeta& m : ft.meta) ctx->print_cache.push_back(make_print_cache(m.key, m.opcode, m.mod_group));
     ctx->field_infos.resize(ft.meta.size());
     for (size_t v = 0; v < ft.meta.size(); ++v) {
         ctx->by_name[{ft.meta[v].key, ft.meta[v].mod_group}] = (uint32_t)v;
@@ -1109,43 +1112,91 @@ struct LoweredBatch {
     std::vector<u128> clear, set;
 };
 
-// Throws TextError carrying the message the reference would report.
+// Host threads for the text layer: printing and lowering are per-instruction and independent.
+unsigned text_threads(uint64_t n) {
+    const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+    return (unsigned)std::min<uint64_t>(std::min(hw, 64u), std::max<uint64_t>(1, n / 2048));
+}
+
+// Runs fn(begin, end, part) over `parts` contiguous ranges of [0, n), one host thread each.
+// An exception in a range is rethrown here; with several, the one of the lowest range.
+template <typename Fn>
+void parallel_ranges(uint64_t n, unsigned parts, Fn fn) {
+    if (parts <= 1) { fn((uint64_t)0, n, 0u); return; }
+    std::vector<std::exception_ptr> errors(parts);
+    std::vector<std::thread> pool;
+    for (unsigned k = 0; k < parts; ++k)
+        pool.emplace_back([&, k] {
+            try {
+                fn(n * k / parts, n * (k + 1) / parts, k);
+            } catch (...) {
+                errors[k] = std::current_exception();
+            }
+        });
+    for (std::thread& th : pool) th.join();
+    for (const std::exception_ptr& e : errors)
+        if (e) std::rethrow_exception(e);
+}
+
+// One instruction -> record + patch appended to `out`.  Throws TextError carrying the message the
+// reference would report.
+void lower_one(const cubit_ctx* ctx, const TextInstruction& insn, int mode, LoweredBatch* out) {
+    LoweredInstruction low;
+    try {
+        low = ctx->text->lower(insn);
+    } catch (const TextError& e) {
+        if (mode == CUBIT_TEXT_ONE) throw TextError(std::string("encode error: ") + e.what());
+        char at[32];
+        snprintf(at, sizeof at, "0x%x", insn.addr);
+        throw TextError(std::string("encode error at addr ") + at + ": " + e.what());
+    }
+    uint32_t slots[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (!low.raw) {
+        const VariantMeta& m = ctx->flat.meta[low.variant];
+        for (size_t k = 0; k < m.fields.size(); ++k) {
+            const FieldMeta& f = m.fields[k];
+            if (f.dst_pos == 0xFFFFFFFFu) continue;
+            put_bits(slots, f.dst_pos, f.stored_bits, low.values[k]);
+        }
+    }
+    out->form.push_back(low.raw ? (uint16_t)0xFFFF : (uint16_t)low.variant);
+    out->slots.insert(out->slots.end(), slots, slots + 8);
+    out->ctrl.push_back(low.ctrl);
+    out->clear.push_back(low.clear);
+    out->set.push_back(low.set);
+}
+
+void append_batch(LoweredBatch* to, const LoweredBatch& from) {
+    to->form.insert(to->form.end(), from.form.begin(), from.form.end());
+    to->slots.insert(to->slots.end(), from.slots.begin(), from.slots.end());
+    to->ctrl.insert(to->ctrl.end(), from.ctrl.begin(), from.ctrl.end());
+    to->clear.insert(to->clear.end(), from.clear.begin(), from.clear.end());
+    to->set.insert(to->set.end(), from.set.begin(), from.set.end());
+}
+
 void lower_text(const cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, LoweredBatch* out) {
-    std::vector<TextInstruction> insns;
     if (mode == CUBIT_TEXT_ONE) {
+        TextInstruction insn;
         try {
-            insns.push_back(parse_sass(text, base_addr));
+            insn = parse_sass(text, base_addr);
         } catch (const TextError& e) {
             throw TextError(std::string("parse error: ") + e.what());
         }
-    } else {
-        insns = parse_program(text, base_addr);
+        lower_one(ctx, insn, mode, out);
+        return;
     }
-    for (const TextInstruction& insn : insns) {
-        LoweredInstruction low;
-        try {
-            low = ctx->text->lower(insn);
-        } catch (const TextError& e) {
-            if (mode == CUBIT_TEXT_ONE) throw TextError(std::string("encode error: ") + e.what());
-            char at[32];
-            snprintf(at, sizeof at, "0x%x", insn.addr);
-            throw TextError(std::string("encode error at addr ") + at + ": " + e.what());
-        }
-        uint32_t slots[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (!low.raw) {
-            const VariantMeta& m = ctx->flat.meta[low.variant];
-            for (size_t k = 0; k < m.fields.size(); ++k) {
-                const FieldMeta& f = m.fields[k];
-                if (f.dst_pos == 0xFFFFFFFFu) continue;
-                put_bits(slots, f.dst_pos, f.stored_bits, low.values[k]);
-            }
-        }
-        out->form.push_back(low.raw ? (uint16_t)0xFFFF : (uint16_t)low.variant);
-        out->slots.insert(out->slots.end(), slots, slots + 8);
-        out->ctrl.push_back(low.ctrl);
-        out->clear.push_back(low.clear);
-        out->set.push_back(low.set);
-    }
+    // Statements are split and labels resolved in one sequential pass; lowering runs in parallel
+    // and reports the failure of the earliest statement, as a sequential pass would.
+    const RangeRunner runner = [](size_t n, const std::function<void(size_t, size_t)>& body) {
+        parallel_ranges(n, text_threads(n), [&](uint64_t b, uint64_t e, unsigned) { body((size_t)b, (size_t)e); });
+    };
+    const std::vector<TextInstruction> insns = parse_program(text, base_addr, runner);
+    const unsigned parts = text_threads(insns.size());
+    std::vector<LoweredBatch> piece(parts);
+    parallel_ranges(insns.size(), parts, [&](uint64_t b, uint64_t e, unsigned k) {
+        for (uint64_t i = b; i < e; ++i) lower_one(ctx, insns[i], mode, &piece[k]);
+    });
+    for (const LoweredBatch& p : piece) append_batch(out, p);
 }
 
 void json_escape(const std::string& s, std::string* out) {
@@ -1308,6 +1359,7 @@ DecodedView view_of_record(const cubit_ctx* ctx, uint32_t form, const uint32_t s
     const VariantMeta& m = ctx->flat.meta[form];
     DecodedView v;
     v.key = m.key; v.mod_group = m.mod_group; v.opcode = m.opcode; v.raw = raw; v.addr = addr;
+    v.cache = &ctx->print_cache[form];
     v.fields.reserve(m.fields.size() + 4);
     for (const FieldMeta& f : m.fields) {
         PrintField pf;
@@ -1367,11 +1419,16 @@ extern "C" int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, u
         const int rc = records_for_print(ctx, words, n, form, slots, ctrl, &f, &s, &c);
         if (rc) return rc;
     }
+    const unsigned parts = text_threads(n);
+    std::vector<std::string> piece(parts);
+    parallel_ranges(n, parts, [&](uint64_t b, uint64_t e, unsigned k) {
+        for (uint64_t i = b; i < e; ++i) {
+            piece[k] += print_word(ctx, (const uint8_t*)words, i, n, base_addr + (uint32_t)(16 * i), form, slots, ctrl);
+            piece[k] += '\n';
+        }
+    });
     std::string text;
-    for (uint64_t i = 0; i < n; ++i) {
-        text += print_word(ctx, (const uint8_t*)words, i, n, base_addr + (uint32_t)(16 * i), form, slots, ctrl);
-        text += '\n';
-    }
+    for (const std::string& p : piece) text += p;
     *needed = text.size() + 1;
     if (out && capacity >= text.size() + 1) memcpy(out, text.c_str(), text.size() + 1);
     return CUBIT_OK;
@@ -1380,6 +1437,31 @@ extern "C" int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, u
 // ---- listings ------------------------------------------------------------------------------
 
 namespace {
+
+// Lowers the printed text of every decodable word (in parallel); `where` lists, in order, the
+// words whose text parsed and found a table entry, `out` their records and patches.
+void lower_printed(const cubit_ctx* ctx, const std::vector<std::string>& text, const std::vector<uint8_t>& unknown,
+                   const std::vector<uint32_t>& addr_of, LoweredBatch* out, std::vector<uint64_t>* where) {
+    const uint64_t total = text.size();
+    const unsigned parts = text_threads(total);
+    std::vector<LoweredBatch> piece(parts);
+    std::vector<std::vector<uint64_t>> piece_where(parts);
+    parallel_ranges(total, parts, [&](uint64_t b, uint64_t e, unsigned k) {
+        for (uint64_t i = b; i < e; ++i) {
+            if (unknown[i]) continue;
+            try {
+                lower_one(ctx, parse_sass(text[i], addr_of[i]), CUBIT_TEXT_ONE, &piece[k]);
+                piece_where[k].push_back(i);
+            } catch (const TextError&) {
+                // does not parse, or no table entry fits
+            }
+        }
+    });
+    for (unsigned k = 0; k < parts; ++k) {
+        append_batch(out, piece[k]);
+        where->insert(where->end(), piece_where[k].begin(), piece_where[k].end());
+    }
+}
 
 std::string strip_statement_end(std::string t) {
     while (t.size() >= 2 && t.compare(t.size() - 2, 2, " ;") == 0) t.erase(t.size() - 2);
@@ -1411,7 +1493,7 @@ bool listing_is_branch(const std::string& text) {
 // Value of the last "0x<hex>" in the text that fits 32 bits: a branch's target operand.
 bool listing_last_hex(const std::string& t, uint32_t* out) {
     bool found = false;
-    for (size_t i = 0; i + 2 < t.size() + 0; ++i) {
+    for (size_t i = 0; i + 2 < t.size(); ++i) {
         if (t[i] != '0' || t[i + 1] != 'x') continue;
         size_t k = i + 2;
         uint64_t v = 0;
@@ -1522,32 +1604,23 @@ extern "C" int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const cha
     }
     std::vector<std::string> text(total);
     std::vector<uint8_t> unknown(total, 0);
+    std::vector<uint32_t> addr_of(total);
     for (size_t k = 0; k < chosen.size(); ++k)
-        for (uint64_t i = start[k]; i < start[k + 1]; ++i) {
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) addr_of[i] = (uint32_t)((i - start[k]) * 16);
+    const unsigned parts = text_threads(total);
+    parallel_ranges(total, parts, [&](uint64_t b, uint64_t e, unsigned) {
+        for (uint64_t i = b; i < e; ++i) {
             unknown[i] = form[i] == 0xFFFFu;
-            text[i] = strip_statement_end(print_word(ctx, words.data(), i, total, (uint32_t)((i - start[k]) * 16),
-                                                     form.data(), slots.data(), ctrl.data()));
+            text[i] = strip_statement_end(print_word(ctx, words.data(), i, total, addr_of[i], form.data(), slots.data(), ctrl.data()));
         }
+    });
     // Frozen listings keep only lines whose text encodes back to the same word outside the
     // scheduling field: lower every line on the host, encode all of them in one batch.
     std::vector<uint8_t> faithful(total, 0);
     if (frozen && total) {
         LoweredBatch b;
         std::vector<uint64_t> where;
-        for (size_t k = 0; k < chosen.size(); ++k)
-            for (uint64_t i = start[k]; i < start[k + 1]; ++i) {
-                if (unknown[i]) continue;
-                try {
-                    LoweredBatch one;
-                    lower_text(ctx, text[i].c_str(), (uint32_t)((i - start[k]) * 16), CUBIT_TEXT_ONE, &one);
-                    b.form.push_back(one.form[0]); b.ctrl.push_back(one.ctrl[0]);
-                    b.slots.insert(b.slots.end(), one.slots.begin(), one.slots.end());
-                    b.clear.push_back(one.clear[0]); b.set.push_back(one.set[0]);
-                    where.push_back(i);
-                } catch (const std::exception&) {
-                    // does not parse or has no table entry: not faithful
-                }
-            }
+        lower_printed(ctx, text, unknown, addr_of, &b, &where);
         const uint64_t m = where.size();
         if (m) {
             std::vector<uint32_t> planes(8 * m);
@@ -1666,24 +1739,20 @@ extern "C" int cubit_patch_elf(cubit_ctx* ctx, const cubit_elf* elf, void* out, 
         if (rc) return rc;
     }
     // decode -> print -> parse -> lower on the host; what lowers is encoded in one batch.
+    std::vector<std::string> text(total);
+    std::vector<uint8_t> unknown(total, 0);
+    std::vector<uint32_t> addr_of(total);
+    for (uint32_t k = 0; k < n_sec; ++k)
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) addr_of[i] = (uint32_t)((i - start[k]) * 16);
+    parallel_ranges(total, text_threads(total), [&](uint64_t b0, uint64_t e0, unsigned) {
+        for (uint64_t i = b0; i < e0; ++i) {
+            unknown[i] = form[i] == 0xFFFFu;
+            if (!unknown[i]) text[i] = print_word(ctx, words.data(), i, total, addr_of[i], form.data(), slots.data(), ctrl.data());
+        }
+    });
     LoweredBatch b;
     std::vector<uint64_t> where;
-    for (uint32_t k = 0; k < n_sec; ++k)
-        for (uint64_t i = start[k]; i < start[k + 1]; ++i) {
-            if (form[i] == 0xFFFFu) continue;
-            const uint32_t addr = (uint32_t)((i - start[k]) * 16);
-            try {
-                const std::string text = print_word(ctx, words.data(), i, total, addr, form.data(), slots.data(), ctrl.data());
-                LoweredBatch one;
-                lower_text(ctx, text.c_str(), addr, CUBIT_TEXT_ONE, &one);
-                b.form.push_back(one.form[0]); b.ctrl.push_back(one.ctrl[0]);
-                b.slots.insert(b.slots.end(), one.slots.begin(), one.slots.end());
-                b.clear.push_back(one.clear[0]); b.set.push_back(one.set[0]);
-                where.push_back(i);
-            } catch (const std::exception&) {
-                // kept as it is
-            }
-        }
+    lower_printed(ctx, text, unknown, addr_of, &b, &where);   // what does not parse or encode is kept as it is
     const uint64_t m = where.size();
     std::vector<uint8_t> enc(16 * m);
     if (m) {

@@ -574,20 +574,10 @@ TextInstruction parse_cuasm_line(const std::string& line_in, uint32_t addr) {
     return parse_sass(line, addr);
 }
 
-std::vector<TextInstruction> parse_program(const std::string& text, uint32_t base_addr) {
-    struct Statement { bool is_label; std::string label; TextInstruction insn; };
-    std::vector<Statement> stmts;
-    uint32_t addr = base_addr;
-    auto push_insn = [&](const std::string& line) {
-        try {
-            TextInstruction insn = parse_cuasm_line(line, addr);
-            insn.addr = addr;
-            addr += 16;
-            stmts.push_back({false, "", std::move(insn)});
-        } catch (const TextError&) {
-            // directives and anything else that is not an instruction are skipped
-        }
-    };
+std::vector<TextInstruction> parse_program(const std::string& text, uint32_t base_addr, const RangeRunner& runner) {
+    // Pass 1 (in order): cut the text into labels and candidate statements.
+    struct Piece { bool is_label; std::string text; };
+    std::vector<Piece> pieces;
     size_t pos = 0;
     while (pos <= text.size()) {
         size_t nl = text.find('\n', pos);
@@ -618,27 +608,44 @@ std::vector<TextInstruction> parse_program(const std::string& text, uint32_t bas
                     if (!is_alnum(line[k]) && line[k] != '_') { is_label = false; break; }
             }
             if (is_label) {
-                stmts.push_back({true, line.substr(0, colon), TextInstruction()});
+                pieces.push_back({true, line.substr(0, colon)});
                 const std::string rest = trim(line.substr(colon + 1));
-                if (!rest.empty()) push_insn(rest);
+                if (!rest.empty()) pieces.push_back({false, rest});
                 continue;
             }
-            push_insn(line);
+            pieces.push_back({false, line});
         }
     }
-    // Labels -> addresses, then branch operands that name a label become targets.
+    // Pass 2 (any order): parse the statements; directives and anything else that is not an
+    // instruction are dropped.
+    std::vector<TextInstruction> parsed(pieces.size());
+    std::vector<uint8_t> ok(pieces.size(), 0);
+    const std::function<void(size_t, size_t)> body = [&](size_t b, size_t e) {
+        for (size_t i = b; i < e; ++i) {
+            if (pieces[i].is_label) continue;
+            try {
+                parsed[i] = parse_cuasm_line(pieces[i].text, 0);
+                ok[i] = 1;
+            } catch (const TextError&) {
+            }
+        }
+    };
+    if (runner) runner(pieces.size(), body);
+    else body(0, pieces.size());
+    // Pass 3 (in order): addresses, labels -> addresses, branch operands that name a label.
     std::unordered_map<std::string, uint32_t> label_addr;
-    uint32_t a = base_addr;
-    for (const Statement& s : stmts) {
-        if (s.is_label) label_addr[s.label] = a;
-        else a += 16;
+    uint32_t addr = base_addr;
+    for (size_t i = 0; i < pieces.size(); ++i) {
+        if (pieces[i].is_label) label_addr[pieces[i].text] = addr;
+        else if (ok[i]) { parsed[i].addr = addr; addr += 16; }
     }
     static const char* const kResolveOps[] = {"BRA", "BSSY", "CALL", "JMP", "RET", "BRX", "BRXU"};
     std::vector<TextInstruction> out;
-    for (Statement& s : stmts) {
-        if (s.is_label) continue;
-        if (in_list(kResolveOps, s.insn.opcode))
-            for (TextOperand& op : s.insn.operands)
+    for (size_t i = 0; i < pieces.size(); ++i) {
+        if (pieces[i].is_label || !ok[i]) continue;
+        TextInstruction& insn = parsed[i];
+        if (in_list(kResolveOps, insn.opcode))
+            for (TextOperand& op : insn.operands)
                 if (op.kind == OperandKind::Label) {
                     const auto it = label_addr.find(op.text);
                     if (it != label_addr.end()) {
@@ -648,7 +655,7 @@ std::vector<TextInstruction> parse_program(const std::string& text, uint32_t bas
                         op = t;
                     }
                 }
-        out.push_back(std::move(s.insn));
+        out.push_back(std::move(insn));
     }
     return out;
 }

@@ -11,6 +11,7 @@
 //     rather than from table fields; the final word is (kernel word & ~clear) | set.
 #pragma once
 #include <cstdint>
+#include <functional>
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
@@ -79,7 +80,10 @@ TextInstruction parse_cuasm_line(const std::string& line, uint32_t addr);
 // Several statements separated by ';' or newlines, with "name:" labels and // or # comments;
 // lines that do not parse are skipped, labels of branch operands resolve to addresses
 // (reference src/parser.rs:485-588, both passes).
-std::vector<TextInstruction> parse_program(const std::string& text, uint32_t base_addr);
+// `runner(n, body)` must call body(begin, end) over ranges covering [0, n), possibly from several
+// threads: statements are parsed independently of one another; null runs them in order here.
+typedef std::function<void(size_t, const std::function<void(size_t, size_t)>&)> RangeRunner;
+std::vector<TextInstruction> parse_program(const std::string& text, uint32_t base_addr, const RangeRunner& runner = nullptr);
 
 // Sorted, comma-joined dot-modifiers of the mnemonic (reference src/table.rs:477-502).
 std::string extract_mod_group(const std::string& sass);
@@ -100,11 +104,20 @@ struct PrintField {
     int32_t token_idx = 0;
     std::string ext;      // extraction name as the decoder reports it (reference src/decoder.rs:679-705)
 };
+// What the printer derives from a variant's names alone; callers that print many words build
+// it once per variant.
+struct VariantPrintCache {
+    std::vector<std::string> op_types;   // operand-type segments of the key (reference src/printer.rs:345-370)
+    std::string mnemonic;                // opcode + ordered modifiers (reference src/printer.rs:430-445)
+};
+VariantPrintCache make_print_cache(const std::string& key, const std::string& opcode, const std::string& mod_group);
+
 struct DecodedView {
     std::string key, mod_group, opcode;
     std::vector<PrintField> fields;
     u128 raw = 0;
     uint32_t addr = 0;
+    const VariantPrintCache* cache = nullptr;   // optional; computed on the fly when null
 };
 // SASS text without the trailing " ;" (reference src/printer.rs:12-212).
 std::string to_sass(const DecodedView& insn);
