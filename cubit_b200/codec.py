@@ -358,11 +358,14 @@ class Codec:
         form = np.ascontiguousarray(form, np.uint16); slots = np.ascontiguousarray(slots, np.uint32)
         ctrl = np.ascontiguousarray(ctrl, np.uint32)
         need = C.c_uint64()
-        self._check(self._lib.cubit_text_print(self._ctx, _ptr(words), n, addr, _ptr(form), _ptr(slots), _ptr(ctrl),
-                                               None, 0, need))
-        buf = C.create_string_buffer(need.value)
-        self._check(self._lib.cubit_text_print(self._ctx, _ptr(words), n, addr, _ptr(form), _ptr(slots), _ptr(ctrl),
-                                               buf, need.value, need))
+        cap = 96 * n + 64                      # nearly always enough; the call reports the exact size otherwise
+        for _ in range(2):
+            buf = C.create_string_buffer(cap)
+            self._check(self._lib.cubit_text_print(self._ctx, _ptr(words), n, addr, _ptr(form), _ptr(slots), _ptr(ctrl),
+                                                   buf, cap, need))
+            if need.value <= cap:
+                break
+            cap = need.value
         return buf.value.decode().split("\n")[:n]
 
     def to_sass(self, lo: int, hi: int, addr: int = 0) -> str:
@@ -466,9 +469,19 @@ class Codec:
         try:
             need, n_raw = C.c_uint64(), C.c_uint64()
             only = kernel.encode() if kernel is not None else None
-            self._check(self._lib.cubit_disassemble(self._ctx, elf, only, int(frozen), None, 0, need, n_raw))
-            out = C.create_string_buffer(need.value)
-            self._check(self._lib.cubit_disassemble(self._ctx, elf, only, int(frozen), out, need.value, need, n_raw))
+            n_text = self._lib.cubit_elf_num_text(elf)
+            size = C.c_uint64()
+            total = 0
+            for i in range(n_text):
+                self._lib.cubit_elf_text(elf, i, None, None, C.byref(size))
+                total += size.value // 16
+            cap = 112 * total + 512 * n_text + 64   # nearly always enough; the call reports the exact size otherwise
+            for _ in range(2):
+                out = C.create_string_buffer(cap)
+                self._check(self._lib.cubit_disassemble(self._ctx, elf, only, int(frozen), out, cap, need, n_raw))
+                if need.value <= cap:
+                    break
+                cap = need.value
         finally:
             self._lib.cubit_elf_free(elf)
         text = out.value.decode()

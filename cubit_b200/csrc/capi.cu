@@ -1640,73 +1640,100 @@ extern "C" int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const cha
         }
     }
 
-    std::vector<std::string> lines;
-    uint64_t raw_lines = 0;
-    char buf[96];
-    for (size_t k = 0; k < chosen.size(); ++k) {
-        if (!lines.empty()) lines.push_back("");
-        const KernelInfo info = kernel_info(elf, sections, names[k]);
-        const uint64_t b0 = start[k], e0 = start[k + 1];
-        if (frozen) {
-            std::vector<uint32_t> targets;
-            uint32_t max_reg = 1;
-            for (uint64_t i = b0; i < e0; ++i) {
+    // Per-word line text, in parallel; per-kernel headers and the final join in order.
+    std::vector<uint32_t> kernel_of(total);
+    for (size_t k = 0; k < chosen.size(); ++k)
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) kernel_of[i] = (uint32_t)k;
+    // Frozen: branch targets and the largest register per word first (both read the text).
+    std::vector<uint8_t> has_target(frozen ? total : 0, 0);
+    std::vector<uint32_t> target(frozen ? total : 0, 0), word_max_reg(frozen ? total : 0, 1);
+    if (frozen)
+        parallel_ranges(total, parts, [&](uint64_t b, uint64_t e, unsigned) {
+            for (uint64_t i = b; i < e; ++i) {
                 uint32_t t;
-                if (!unknown[i] && listing_is_branch(text[i]) && listing_last_hex(text[i], &t)) targets.push_back(t);
-                max_reg = listing_max_reg(text[i], max_reg);
+                if (!unknown[i] && listing_is_branch(text[i]) && listing_last_hex(text[i], &t)) { has_target[i] = 1; target[i] = t; }
+                word_max_reg[i] = listing_max_reg(text[i], 1);
             }
-            std::sort(targets.begin(), targets.end());
-            lines.push_back(".entry " + names[k]);
-            lines.push_back("    .reg R0-R" + std::to_string(std::min(max_reg + 4, 255u)));
+        });
+    std::vector<std::vector<uint32_t>> targets(frozen ? chosen.size() : 0);
+    std::vector<uint32_t> max_reg(chosen.size(), 1);
+    if (frozen)
+        for (size_t k = 0; k < chosen.size(); ++k) {
+            for (uint64_t i = start[k]; i < start[k + 1]; ++i) {
+                if (has_target[i]) targets[k].push_back(target[i]);
+                max_reg[k] = std::max(max_reg[k], word_max_reg[i]);
+            }
+            std::sort(targets[k].begin(), targets[k].end());
+        }
+    std::vector<std::string> body(total);
+    std::vector<uint64_t> raw_count(std::max(parts, 1u), 0);
+    parallel_ranges(total, parts, [&](uint64_t b, uint64_t e, unsigned part) {
+        char buf[96];
+        for (uint64_t i = b; i < e; ++i) {
+            const uint32_t addr = addr_of[i];
+            u128 w;
+            memcpy(&w, words.data() + i * 16, 16);
+            if (!frozen) {
+                snprintf(buf, sizeof buf, "  /*%04x*/  ", addr);
+                if (unknown[i]) { body[i] = buf + text[i]; ++raw_count[part]; continue; }
+                char tail[48];
+                snprintf(tail, sizeof tail, " /* @sched 0x%05x */ ;", (uint32_t)((w >> 105) & 0x1FFFF));
+                body[i] = buf + text[i] + tail;
+                continue;
+            }
+            const std::vector<uint32_t>& tg = targets[kernel_of[i]];
+            std::string label = "    ";
+            if (std::binary_search(tg.begin(), tg.end(), addr)) {
+                snprintf(buf, sizeof buf, "L_%x:  ", addr);
+                label = buf;
+            }
+            if (unknown[i] || !faithful[i]) {
+                body[i] = label + "__raw__0x" + hex_word(w) + " ;";
+                ++raw_count[part];
+                continue;
+            }
+            const std::string cc = format_control_code(unpack_control_code((uint32_t)((w >> 105) & 0x1FFFF)));
+            std::string t = text[i];
+            if (has_target[i]) {
+                snprintf(buf, sizeof buf, "0x%x", target[i]);
+                const size_t pos = t.rfind(buf);
+                if (pos != std::string::npos) {
+                    char lab[32];
+                    snprintf(lab, sizeof lab, "L_%x", target[i]);
+                    t.replace(pos, strlen(buf), lab);
+                }
+            }
+            body[i] = label + "[" + cc + "] " + t + " ;";
+        }
+    });
+    uint64_t raw_lines = 0;
+    for (uint64_t c : raw_count) raw_lines += c;
+    size_t bytes = 1;
+    for (const std::string& l : body) bytes += l.size() + 1;
+    std::string listing;
+    listing.reserve(bytes + chosen.size() * 256);
+    bool first_line = true;
+    auto put = [&](const std::string& l) {
+        if (!first_line) listing += '\n';
+        listing += l;
+        first_line = false;
+    };
+    for (size_t k = 0; k < chosen.size(); ++k) {
+        if (!first_line) put("");
+        const KernelInfo info = kernel_info(elf, sections, names[k]);
+        if (frozen) {
+            put(".entry " + names[k]);
+            put("    .reg R0-R" + std::to_string(std::min(max_reg[k] + 4, 255u)));
             std::vector<std::pair<uint32_t, uint32_t>> params = info.params;
             std::stable_sort(params.begin(), params.end(), [](const auto& a, const auto& b) { return a.first < b.first; });
             for (size_t p = 0; p < params.size(); ++p)
-                lines.push_back(std::string("    .param ") + (params[p].second > 4 ? "u64" : "u32") + " p" + std::to_string(p));
-            if (info.shared_size > 0) lines.push_back("    .shared smem[" + std::to_string(info.shared_size) + "]");
-            for (uint64_t i = b0; i < e0; ++i) {
-                const uint32_t addr = (uint32_t)((i - b0) * 16);
-                u128 w;
-                memcpy(&w, words.data() + i * 16, 16);
-                std::string label = "    ";
-                if (std::binary_search(targets.begin(), targets.end(), addr)) {
-                    snprintf(buf, sizeof buf, "L_%x:  ", addr);
-                    label = buf;
-                }
-                if (unknown[i] || !faithful[i]) {
-                    lines.push_back(label + "__raw__0x" + hex_word(w) + " ;");
-                    ++raw_lines;
-                    continue;
-                }
-                const std::string cc = format_control_code(unpack_control_code((uint32_t)((w >> 105) & 0x1FFFF)));
-                std::string t = text[i];
-                uint32_t target;
-                if (listing_is_branch(t) && listing_last_hex(t, &target)) {
-                    snprintf(buf, sizeof buf, "0x%x", target);
-                    const size_t pos = t.rfind(buf);
-                    if (pos != std::string::npos) {
-                        char lab[32];
-                        snprintf(lab, sizeof lab, "L_%x", target);
-                        t.replace(pos, strlen(buf), lab);
-                    }
-                }
-                lines.push_back(label + "[" + cc + "] " + t + " ;");
-            }
+                put(std::string("    .param ") + (params[p].second > 4 ? "u64" : "u32") + " p" + std::to_string(p));
         } else {
-            lines.push_back("// " + names[k]);
-            if (info.shared_size > 0) lines.push_back("    .shared smem[" + std::to_string(info.shared_size) + "]");
-            for (uint64_t i = b0; i < e0; ++i) {
-                u128 w;
-                memcpy(&w, words.data() + i * 16, 16);
-                snprintf(buf, sizeof buf, "  /*%04x*/  ", (uint32_t)((i - b0) * 16));
-                if (unknown[i]) { lines.push_back(buf + text[i]); ++raw_lines; continue; }
-                char tail[48];
-                snprintf(tail, sizeof tail, " /* @sched 0x%05x */ ;", (uint32_t)((w >> 105) & 0x1FFFF));
-                lines.push_back(buf + text[i] + tail);
-            }
+            put("// " + names[k]);
         }
+        if (info.shared_size > 0) put("    .shared smem[" + std::to_string(info.shared_size) + "]");
+        for (uint64_t i = start[k]; i < start[k + 1]; ++i) put(body[i]);
     }
-    std::string listing;
-    for (size_t i = 0; i < lines.size(); ++i) { if (i) listing += '\n'; listing += lines[i]; }
     listing += '\n';
     if (n_raw) *n_raw = raw_lines;
     *needed = listing.size() + 1;
