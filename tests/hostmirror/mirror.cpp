@@ -62,11 +62,11 @@ void mir_info(void* h, uint32_t* out) {
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
 // The compiled table blob and its section offsets (BlobLayout as 24 u32).
-void mir_blob(void* h, const uint32_t** blob, uint32_t* layout24) {
+void mir_blob(void* h, const uint32_t** blob, uint32_t* layout_words) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
     static_assert(sizeof(BlobLayout) == 26 * sizeof(uint32_t), "layout size");
-    memcpy(layout24, &m->flat.at, sizeof(BlobLayout));
+    memcpy(layout_words, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
 void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_classes, uint8_t* n_match, uint8_t* depth) {
