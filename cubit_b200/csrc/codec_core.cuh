@@ -127,6 +127,14 @@ enum : uint32_t {
 //   [7:0] position in canonical order (last tie-break)
 enum { KEY_PRIO_POS = 29, KEY_POPC_POS = 15, KEY_TUPLE_SHIFT = 8 };
 
+// Ranking memo.  Inside a leaf of at most MEMO_MAX_CLASSES classes whose word-dependent rank
+// part reads nothing but the guard nibble (and_base bits outside the strict mask all lie in
+// bits 15:12), the top-ranked candidate is a function of (guard nibble, set of strictly
+// matching classes).  The table compiler evaluates the ranking loop for every such pair and
+// stores winner and tie flag in one byte; in those leaves CR_GROUP carries the leaf's memo
+// number + 1 above its low MEMO_MAX_CLASSES bits.
+enum : uint32_t { MEMO_MAX_CLASSES = 6, MEMO_BYTES = 16u << MEMO_MAX_CLASSES, MEMO_TIE = 0x80u, MEMO_WINNER_MASK = 0x1Fu };
+
 enum {                      // extraction record, 8 u32, hot; variants with the same field layout share one
     XR_DESC = 0,            // [0..3] eight u16 slot descriptors: source shift | bits << 7 (bits 0..32)
     XR_MASK = 4,            // [4..6] layout 0: 1-bit field positions per limb; layout 1: all field bits per limb
@@ -190,6 +198,7 @@ struct BlobLayout {
     uint32_t var[2];      // variant records (encode side, two quad planes) directly follow the deposit records
     uint32_t enc_end;     // encode window: [enc, enc_end) holds the deposit and variant records
     uint32_t flagbest, gfields, metaf;
+    uint32_t memo;        // ranking memo: MEMO_BYTES per memo leaf, one byte per (guard nibble, strict-match mask)
     uint32_t rt[2];       // roundtrip constants per variant: {A0, A1, A2, E3} and {~M0, ~M1, ~M2, reuse keep | const << 3}
     uint32_t total_words;
     uint32_t n_variants;
@@ -490,15 +499,30 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         }
         if (base == 0) { strict0 = strict; broad0 = broad; }
         uint32_t mm = strict | broad;
-        if (count <= 32 && broad == 0 && strict) {
+        if (count <= 32 && strict) {
+            // Strict matches outrank broad ones of the same score sign, and classes are stored by
+            // (score sign, ...): when the first strict match has a non-negative score no broad
+            // match can be on top, and the strict matches are ranked among themselves.
             const uint32_t f = cb_lowest_bit(strict);
+            const Quad q2f = HOT::q(t, t.at.classes[2] + (r0 + f) * 4u);
+            if (broad == 0 || !(q2f.x >> 31)) {
             const Quad q3 = HOT::q(t, t.at.classes[3] + (r0 + f) * 4u);
-            mm = q3.w & strict;
+            const bool small = count <= MEMO_MAX_CLASSES;
+            const uint32_t memo = small ? (q3.w >> MEMO_MAX_CLASSES) : 0u;
+            mm = (small ? (q3.w & ((1u << MEMO_MAX_CLASSES) - 1u)) : q3.w) & strict;
             if (mm == (1u << f)) {
-                const Quad q1 = HOT::q(t, t.at.classes[1] + (r0 + f) * 4u), q2 = HOT::q(t, t.at.classes[2] + (r0 + f) * 4u);
-                first_key = q2.x; first_fl = q2.y; first_best = q2.z;
+                const Quad q1 = HOT::q(t, t.at.classes[1] + (r0 + f) * 4u);
+                first_key = q2f.x; first_fl = q2f.y; first_best = q2f.z;
                 tie_first = (q1.z & CI_TIE_WITHIN) ? 1u : 0u;
                 mm = 0;
+            } else if (memo) {
+                const uint32_t at = (memo - 1u) * MEMO_BYTES + ((((c0 >> 12) & 15u) << MEMO_MAX_CLASSES) | strict);
+                const uint32_t e = (cb_ld(t.cold + t.at.memo + (at >> 2)) >> (8u * (at & 3u))) & 0xFFu;
+                const Quad q2 = HOT::q(t, t.at.classes[2] + (r0 + (e & MEMO_WINNER_MASK)) * 4u);
+                first_key = q2.x; first_fl = q2.y; first_best = q2.z;
+                tie_first = (e & MEMO_TIE) ? 1u : 0u;
+                mm = 0;
+            }
             }
         }
         for (; mm; mm &= mm - 1u) {

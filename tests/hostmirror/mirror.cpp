@@ -65,7 +65,7 @@ void mir_info(void* h, uint32_t* out) {
 void mir_blob(void* h, const uint32_t** blob, uint32_t* layout_words) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 26 * sizeof(uint32_t), "layout size");
+    static_assert(sizeof(BlobLayout) == 27 * sizeof(uint32_t), "layout size");
     memcpy(layout_words, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
@@ -143,10 +143,12 @@ void mir_rank_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* loop_le
             strict |= (prio == 0) << k; broad |= (prio == 2) << k;
         }
         uint32_t mm = strict | broad;
-        if (broad == 0 && strict) {
+        if (strict && (broad == 0 || !(HotPlain::q(t, t.at.classes[2] + (start + cb_lowest_bit(strict)) * 4u).x >> 31))) {
             const uint32_t f = cb_lowest_bit(strict);
-            mm = HotPlain::q(t, t.at.classes[3] + (start + f) * 4u).w & strict;
-            if (mm == (1u << f)) mm = 0;
+            const uint32_t gw = HotPlain::q(t, t.at.classes[3] + (start + f) * 4u).w;
+            const bool small = count <= MEMO_MAX_CLASSES;
+            mm = (small ? (gw & ((1u << MEMO_MAX_CLASSES) - 1u)) : gw) & strict;
+            if (mm == (1u << f) || (small && (gw >> MEMO_MAX_CLASSES))) mm = 0;
         }
         loop_len[i] = (uint8_t)__builtin_popcount(mm);
     }
