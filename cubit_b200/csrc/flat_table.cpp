@@ -260,7 +260,7 @@ struct TreeBuilder {
             rec[CR_INFO] = info;
             rec[CR_GROUP] = group_mask;
             rec[CR_FIRST_FLAGS] = best.flags;
-            rec[CR_KEY] = key_of[mem[0]];
+            rec[CR_KEY] = key_of[mem[0]] | ((info & CI_TIE_WITHIN) ? (uint32_t)KEY_WITHIN : 0u);
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
             uint32_t any = 0, tie_flags = 0;
             for (uint32_t v : mem) any |= st[v].flags & 0xFFFFu;
@@ -282,7 +282,7 @@ struct TreeBuilder {
             }
             rec[CR_ANY_FLAGS] = any | (tie_flags << 16);
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
-            leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY]; leaf_within[ci] = (info & CI_TIE_WITHIN) ? 1u : 0u;
+            leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = (info & CI_TIE_WITHIN) ? 1u : 0u;
         }
         // Ranking memo: when some pair of the leaf is not settled by position and the word-dependent
         // part of every strictly matchable class reads only the guard nibble, run the ranking loop

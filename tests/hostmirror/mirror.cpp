@@ -118,7 +118,7 @@ void mir_rule_stats(void* h, const uint32_t* words, uint64_t n, uint32_t* need_o
             if (prio == 3) continue;
             const uint32_t r = (start + k) * 4;
             const Quad q2 = HotPlain::q(t, t.at.classes[2] + r), q3 = HotPlain::q(t, t.at.classes[3] + r);
-            const uint32_t key = q2.x | dynamic_key(q3, prio, c0, c1, c2);
+            const uint32_t key = (q2.x & ~KEY_WITHIN) | dynamic_key(q3, prio, c0, c1, c2);
             any |= fl;
             if (key < first_key) { first_key = key; first_fl = q2.y; }
         }
