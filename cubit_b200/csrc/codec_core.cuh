@@ -475,16 +475,28 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     for (uint32_t base = 0; base < count; base += 32) {
         const uint32_t chunk = (count - base) < 32u ? (count - base) : 32u;
         const uint32_t r0 = start + base;
-        uint32_t strict = 0, broad = 0;
+        // Strict tests for every class first; the classes that failed but have a broad record are
+        // tested in a loop of their own (one word in three has one; inside the first loop the
+        // branch would be taken by some lane of the warp in nearly every iteration).
+        uint32_t strict = 0, broad = 0, pending = 0;
         {
             uint32_t bit = 1u;
             for (uint32_t i = 0; i < chunk; ++i, bit <<= 1) {
-                uint32_t fl;
-                const uint32_t prio = class_match<HOT>(t, r0 + i, c0, c1, c2, &fl);
-                strict |= prio == 0 ? bit : 0u;
-                broad |= prio == 2 ? bit : 0u;
-                any |= prio != 3 ? fl : 0u;
+                const Quad a = HOT::q(t, t.at.classes[0] + (r0 + i) * 4u), b = HOT::q(t, t.at.classes[1] + (r0 + i) * 4u);
+                const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
+                strict |= hit ? bit : 0u;
+                any |= hit ? b.w : 0u;
+                pending |= (!hit && (b.z & CI_HAS_BROAD)) ? bit : 0u;
             }
+        }
+        for (; pending; pending &= pending - 1u) {
+            const uint32_t i = cb_lowest_bit(pending);
+            const Quad b = HOT::q(t, t.at.classes[1] + (r0 + i) * 4u);
+            const uint32_t br = (b.z & CI_BROAD_MASK) * 4u;
+            const Quad m = HOT::q(t, t.at.broad[0] + br), v = HOT::q(t, t.at.broad[1] + br);
+            const bool hit = (((c0 & m.x) ^ m.w) | ((c1 & m.y) ^ v.x) | ((c2 & m.z) ^ v.y)) == 0;
+            broad |= hit ? (1u << i) : 0u;
+            any |= hit ? b.w : 0u;
         }
         if (base == 0) { strict0 = strict; broad0 = broad; }
         uint32_t mm = strict | broad;
