@@ -130,9 +130,12 @@ def run_cubin(args, rank, world, local):
 DEFAULT_WORDS = 64 * 1024 * 1024    # 1 GiB of 16-byte words
 STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per decoded word from the ncu capture summarised in
-# profiles/decode_kernel_zipf.md: (268.7 MB + 580.7 MB) / 16 Mi words of the captured launch.
-NCU_DRAM_BYTES_PER_WORD = 50.6
+# dram__bytes_read.sum + dram__bytes_write.sum per word of one captured launch, from the ncu summaries
+# under profiles/ (smaller cases than the bench's, scaled by the word count: the traffic is the
+# stream itself, read and written once).  decode: (268.7 MB + 580.7 MB) / 16 Mi words;
+# encode: (319.0 MB + 99.8 MB) / 8 Mi; roundtrip: (134.5 MB + 6.2 MB) / 8 Mi.  Part of the last
+# writes of a captured launch is still in L2 when it ends, more so in the smaller captures.
+NCU_DRAM_BYTES_PER_WORD = {"decode": 50.6, "encode": 49.9, "roundtrip": 16.8}
 
 
 def env_int(name, default):
@@ -405,8 +408,8 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_kind": f"of {peak_kind}", "kernel": wl["kernel"], "kernel_ms": kernel_ms,
                              "bytes_per_insn": wl["bytes"],
-                             "traffic": None if (NCU_DRAM_BYTES_PER_WORD is None or args.workload != "decode")
-                             else NCU_DRAM_BYTES_PER_WORD * n},
+                             "traffic": NCU_DRAM_BYTES_PER_WORD[args.workload] * n
+                             if args.workload in NCU_DRAM_BYTES_PER_WORD else None},
                 "counts": counts, "clocks": clocks}
         if cpu:
             line["cpu_baseline"] = cpu
