@@ -74,6 +74,7 @@ SIGNATURES = {
                                    C.c_void_p, C.c_void_p, C.c_void_p, u64p]),
     "cubit_text_encode": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_int, C.c_uint64, C.c_void_p, u64p]),
     "cubit_text_parse": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64, u64p]),
+    "cubit_listing_assemble": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_void_p, C.c_uint64, u64p, u64p]),
     "cubit_patch_elf": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, u64p, C.POINTER(PatchStats)]),
     "cubit_elf_patch_text": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
     "cubit_disassemble": (C.c_int, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_int, C.c_char_p, C.c_uint64, u64p, u64p]),

@@ -487,6 +487,18 @@ class Codec:
         text = out.value.decode()
         return (text, int(n_raw.value)) if want_raw_count else text
 
+    def assemble_listing(self, listing: str, kernel: str, want_failed: bool = False):
+        """Code bytes of `kernel` from a plain listing as `disassemble` writes it (the encode loop of the
+        reference's listing assembler, src/main.rs:997-1075): every line is encoded at its address, the
+        "@sched" value replaces the scheduling field, placeholder comments give their raw word."""
+        need, failed = C.c_uint64(), C.c_uint64()
+        raw = listing.encode()
+        self._check(self._lib.cubit_listing_assemble(self._ctx, raw, kernel.encode(), None, 0, need, failed))
+        out = np.zeros(max(int(need.value), 1), np.uint8)
+        self._check(self._lib.cubit_listing_assemble(self._ctx, raw, kernel.encode(), _ptr(out), len(out), need, failed))
+        code = out[:int(need.value)].tobytes()
+        return (code, int(failed.value)) if want_failed else code
+
     def patch(self, data: bytes) -> tuple[bytes, dict]:
         """The reference's `patch` over a cubin image (src/main.rs:691-764): every instruction goes
         decode -> print -> parse -> encode and, where that works, gets its low 64 bits rewritten

@@ -293,6 +293,21 @@ int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, uint32_t bas
 int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const char* only_kernel, int frozen, char* out,
                       uint64_t capacity, uint64_t* needed, uint64_t* n_raw);
 
+/* Replaces the encode loop of the reference's listing assembler (parse_sass_file_full,
+ * src/main.rs:225-268, and cmd_asm_build_elf, src/main.rs:997-1075): reads a plain listing as
+ * cubit_disassemble(frozen = 0) writes it -- "// <kernel>" headers, one
+ * "  / *addr* /  <text> / * @sched 0x..... * / ;" line per instruction (comment marks without the
+ * spaces), placeholder comments for undecodable words -- and produces the code bytes of `kernel`:
+ * every line is parsed and encoded at its own address (one batch on the GPU), the "@sched" value
+ * replaces the scheduling field (a line without one gets the reference's default dependency
+ * rule: write barrier 1 when the first operand is a register, the instruction has no guard and
+ * is not a store, branch or barrier, src/main.rs:766-783), a placeholder line contributes its raw
+ * word.  Lines that do not parse or encode leave zero bytes and are counted in *n_failed.
+ * The result is what cubit_elf_patch_text splices into a template cubin.  *needed is the code
+ * length (highest address + 16); nothing is written when it exceeds capacity. */
+int cubit_listing_assemble(cubit_ctx* ctx, const char* listing, const char* kernel, void* code, uint64_t capacity,
+                           uint64_t* needed, uint64_t* n_failed);
+
 /* ---- cubin rewriting ----------------------------------------------------------------------- */
 
 typedef struct {
