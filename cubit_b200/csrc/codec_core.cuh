@@ -481,6 +481,7 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         uint32_t strict = 0, broad = 0, pending = 0;
         {
             uint32_t bit = 1u;
+#pragma unroll 2
             for (uint32_t i = 0; i < chunk; ++i, bit <<= 1) {
                 const Quad a = HOT::q(t, t.at.classes[0] + (r0 + i) * 4u), b = HOT::q(t, t.at.classes[1] + (r0 + i) * 4u);
                 const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
