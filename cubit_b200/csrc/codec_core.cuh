@@ -37,7 +37,7 @@ namespace cubit {
 
 // ---- flat table records ------------------------------------------------------------
 //
-// Lookup structure: dir16[word bits 11:0] -> bucket -> ref.  A ref is a leaf (a run of
+// Lookup structure: dir[word bits 11:0] -> ref.  A ref is a leaf (a run of
 // classes to test), a hash node or a bit node.  A hash node holds the mask bits that every
 // candidate below it checks; candidates that disagree on those bits cannot both match, so
 // the masked word is hashed (perfect hash, found on the host) into a child table of refs.
@@ -63,8 +63,9 @@ CB_HD uint32_t ref_count(uint32_t r) { return (r >> 20) & 0xFFu; }
 enum {                      // hash node record, 8 u32 (two quads)
     NR_MASK = 0,            // [0..2] bits hashed at this node
     NR_MULT = 3,
-    NR_CFG = 4,             // shift | rot1 << 5 | rot2 << 10
+    NR_ROT = 4,             // rot1 | rot2 << 5 (a rotate reads the low five bits of its amount)
     NR_CHILD = 5,           // first entry of the child table
+    NR_SHIFT = 6,           // 32 - log2(child table size)
     NR_WORDS = 8,
 };
 
@@ -72,8 +73,8 @@ enum {                      // class record, 16 u32 (four quads), hot; classes o
     CR_SMASK = 0,           // [0..2] strict match mask (guard bits 15:12 cleared)
     CR_SBASE = 3,           // [3..5] and_base & strict mask
     CR_INFO = 6,            // broad record index | has_broad << 12 | members << 13 | tie_within << 21
-    CR_ANY_FLAGS = 7,       // [15:0] OR of the members' choice flags; [31:16] per flag: the best member
-                            // carrying it shares its rank tuple with another member carrying it
+    CR_ANY_FLAGS = 7,       // [15:0] OR of the members' choice flags; [31:16] in the first class of a leaf: which of
+                            // the leaf's first 16 classes have a broad record
     CR_KEY = 8,             // static rank key of the best member
     CR_FIRST_FLAGS = 9,     // flags of the best member
     CR_BEST = 10,           // best member: variant | extraction record index << 16
@@ -190,8 +191,7 @@ enum { GC_UNIFORM = 0, GC_UREG = 1, GC_MOD8 = 2, GC_REG = 3, GF_NOT_STORED = 0x1
 
 // Blob header: section offsets in u32 units from the start of the blob.
 struct BlobLayout {
-    uint32_t dir16;       // 4096 u16 (two per u32): bucket number + 1, 0 = no variant has these opcode bits
-    uint32_t bucket_ref;  // one ref per bucket
+    uint32_t dir;         // 4096 refs by opcode bits 11:0; 0 = no variant has these opcode bits
     // Records wider than 16 bytes are stored quad by quad (all first quads, then all second
     // quads, ...): a 16-byte stride spreads records over eight bank groups of shared memory.
     uint32_t nodes[2], children, classes[4], broad[2], ext[2];
@@ -306,6 +306,14 @@ CB_HD uint32_t cb_rotl(uint32_t x, uint32_t r) {
 #endif
 }
 CB_HD uint32_t cb_rotr(uint32_t x, uint32_t r) { return cb_rotl(x, (32u - r) & 31u); }
+// x >> (n mod 32): the shift reads the low five bits of its amount.
+CB_HD uint32_t cb_shr_wrap(uint32_t x, uint32_t n) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_r(x, 0u, n);
+#else
+    return x >> (n & 31u);
+#endif
+}
 
 // Cold data: read-only global memory on the device.
 CB_HD uint32_t cb_ld(const uint32_t* p) {
@@ -341,23 +349,20 @@ CB_HD uint32_t cb_extract(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t src, u
 // the word's opcode bits, otherwise ST_OK with the (possibly empty) run of classes.
 template <class HOT>
 CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t* start, uint32_t* count) {
-    const uint32_t op = c0 & 0xFFFu;
-    const uint32_t bucket = (HOT::w(t, t.at.dir16 + (op >> 1)) >> (16 * (op & 1))) & 0xFFFFu;
     *start = 0; *count = 0;
-    if (bucket == 0) return ST_NO_OPCODE;
-    uint32_t ref = HOT::w(t, t.at.bucket_ref + bucket - 1);
+    uint32_t ref = HOT::w(t, t.at.dir + (c0 & 0xFFFu));
+    if (ref == 0) return ST_NO_OPCODE;
     while (!(ref & REF_LEAF)) {
         uint32_t child;
         if (ref & REF_BIT) {
             const uint32_t bit = (ref >> 20) & 127u, w = bit >> 5;
             const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
-            child = ref_index(ref) + ((limb >> (bit & 31u)) & 1u);
+            child = ref_index(ref) + (cb_shr_wrap(limb, bit) & 1u);
         } else {
             const uint32_t n = ref_index(ref) * 4u;
             const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
-            const uint32_t cfg = b.x;
-            const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, (cfg >> 5) & 31u) ^ cb_rotl(c2 & a.z, (cfg >> 10) & 31u);
-            child = b.y + ((f * a.w) >> (cfg & 31u));
+            const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.x >> 5);
+            child = b.y + ((f * a.w) >> b.z);
         }
         ref = HOT::w(t, t.at.children + child);
     }
@@ -441,7 +446,8 @@ CB_HD void fold_flagged(const FlatView& t, uint32_t ci, uint32_t prio, uint32_t 
         const uint32_t f = cb_lowest_bit(need);
         const uint32_t* e = t.cold + t.at.flagbest + q2.w * FB_WORDS + 2u * f;
         key = cb_ld(e); best = cb_ld(e + 1);
-        within = (q1.w >> (16u + f)) & 1u;
+        within = (key & KEY_WITHIN) ? 1u : 0u;
+        key &= ~KEY_WITHIN;
     }
     const uint32_t k = key | dynamic_key(q3, prio, c0, c1, c2);
     if ((k >> KEY_TUPLE_SHIFT) == (*win_key >> KEY_TUPLE_SHIFT)) {
@@ -477,8 +483,11 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         const uint32_t r0 = start + base;
         // Strict tests for every class first; the classes that failed but have a broad record are
         // tested in a loop of their own (one word in three has one; inside the first loop the
-        // branch would be taken by some lane of the warp in nearly every iteration).
+        // branch would be taken by some lane of the warp in nearly every iteration).  Which
+        // classes of the leaf have a broad record is a constant of the leaf, kept in the upper
+        // half of the first class's flag word for leaves of at most 16 classes.
         uint32_t strict = 0, broad = 0, pending = 0;
+        const uint32_t leaf_broad = HOT::w(t, t.at.classes[1] + r0 * 4u + 3u) >> 16;
         {
             uint32_t bit = 1u;
 #pragma unroll 2
@@ -487,8 +496,13 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
                 const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
                 strict |= hit ? bit : 0u;
                 any |= hit ? b.w : 0u;
-                pending |= (!hit && (b.z & CI_HAS_BROAD)) ? bit : 0u;
             }
+        }
+        if (count <= 16) {
+            pending = leaf_broad & ~strict;
+        } else {
+            for (uint32_t i = 0; i < chunk; ++i)
+                if (!((strict >> i) & 1u) && (HOT::w(t, t.at.classes[1] + (r0 + i) * 4u + 2u) & CI_HAS_BROAD)) pending |= 1u << i;
         }
         for (; pending; pending &= pending - 1u) {
             const uint32_t i = cb_lowest_bit(pending);

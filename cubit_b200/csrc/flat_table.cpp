@@ -227,6 +227,7 @@ struct TreeBuilder {
             return std::get<1>(ka) == std::get<1>(kb) && (std::get<2>(ka) >> 8) == (std::get<2>(kb) >> 8);
         };
         std::vector<uint32_t> leaf_group(order.size()), leaf_key(order.size()), leaf_within(order.size());
+        uint32_t leaf_broad16 = 0;   // which of the first 16 classes have a broad record
         for (size_t ci = 0; ci < order.size(); ++ci) {
             const ClassKey& ck = order[ci];
             std::vector<uint32_t>& mem = groups[ck];
@@ -262,7 +263,7 @@ struct TreeBuilder {
             rec[CR_FIRST_FLAGS] = best.flags;
             rec[CR_KEY] = key_of[mem[0]] | ((info & CI_TIE_WITHIN) ? (uint32_t)KEY_WITHIN : 0u);
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
-            uint32_t any = 0, tie_flags = 0;
+            uint32_t any = 0;
             for (uint32_t v : mem) any |= st[v].flags & 0xFFFFu;
             if (mem.size() > 1) {
                 // Best member per choice flag (members are in rank order) and whether it is tied.
@@ -274,16 +275,18 @@ struct TreeBuilder {
                     for (uint32_t v : mem) {
                         if (!((st[v].flags >> f) & 1u)) continue;
                         if (seen == 0) { first_key = key_of[v]; fb[2 * f] = key_of[v]; fb[2 * f + 1] = v | (ext_of[v] << 16); }
-                        else if (seen == 1 && (key_of[v] >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT)) tie_flags |= 1u << f;
+                        else if (seen == 1 && (key_of[v] >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT)) fb[2 * f] |= KEY_WITHIN;
                         ++seen;
                     }
                 }
                 ft.flagbest.insert(ft.flagbest.end(), fb, fb + FB_WORDS);
             }
-            rec[CR_ANY_FLAGS] = any | (tie_flags << 16);
+            rec[CR_ANY_FLAGS] = any;
+            if (ci < 16 && (info & CI_HAS_BROAD)) leaf_broad16 |= 1u << ci;
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
             leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = (info & CI_TIE_WITHIN) ? 1u : 0u;
         }
+        if (!order.empty()) ft.classes[size_t(first_class) * CR_WORDS + CR_ANY_FLAGS] |= leaf_broad16 << 16;
         // Ranking memo: when some pair of the leaf is not settled by position and the word-dependent
         // part of every strictly matchable class reads only the guard nibble, run the ranking loop
         // of the kernel here for every (guard nibble, set of strict matches).
@@ -377,8 +380,9 @@ struct TreeBuilder {
                 uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
                 for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
                 n[NR_MULT] = mult;
-                n[NR_CFG] = (32 - bits) | (r1 << 5) | (r2 << 10);
+                n[NR_ROT] = r1 | (r2 << 5);
                 n[NR_CHILD] = child_base;
+                n[NR_SHIFT] = 32 - bits;
                 return REF_NODE | node;
             }
             // No perfect hash found: fall through and scan (still correct).
@@ -800,14 +804,13 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         ft.max_bucket = std::max(ft.max_bucket, ++bucket_size[b]);
         if (st[vi].matchable()) buckets[b].push_back(uint32_t(vi));
     }
-    std::vector<uint32_t> dir16(2048, 0), bucket_ref;
+    std::vector<uint32_t> dir(4096, 0);
     TreeBuilder tb{st, ext_of, ft};
     tb.class_budget = 2 * nv + 256;
     for (size_t b = 0; b < 4096; ++b) {
         if (!bucket_size[b]) continue;
         ++ft.n_buckets;
-        bucket_ref.push_back(buckets[b].empty() ? uint32_t(REF_LEAF) : tb.build(buckets[b], 0xFFF, 0));
-        dir16[b >> 1] |= uint32_t(bucket_ref.size()) << (16 * (b & 1));
+        dir[b] = buckets[b].empty() ? uint32_t(REF_LEAF) : tb.build(buckets[b], 0xFFF, 0);
     }
     ft.max_depth = tb.max_depth;
     if (ft.broad.empty()) ft.broad.assign(BR_WORDS, 0);
@@ -820,8 +823,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         return at;
     };
     BlobLayout& L = ft.at;
-    L.dir16 = place(dir16);
-    L.bucket_ref = place(bucket_ref);
+    L.dir = place(dir);
     // Quad `q` of every record of a section whose records are `words` wide.
     auto quad_plane = [](const std::vector<uint32_t>& src, size_t words, size_t q) {
         std::vector<uint32_t> out;

@@ -65,7 +65,7 @@ void mir_info(void* h, uint32_t* out) {
 void mir_blob(void* h, const uint32_t** blob, uint32_t* layout_words) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 27 * sizeof(uint32_t), "layout size");
+    static_assert(sizeof(BlobLayout) == 26 * sizeof(uint32_t), "layout size");
     memcpy(layout_words, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
@@ -75,10 +75,8 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
     for (uint64_t i = 0; i < n; ++i) {
         const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
         uint32_t start = 0, count = 0, steps = 0;
-        const uint32_t op = c0 & 0xFFFu;
-        const uint32_t bucket = (t.hot[t.at.dir16 + (op >> 1)] >> (16 * (op & 1))) & 0xFFFFu;
-        if (bucket) {
-            uint32_t ref = t.hot[t.at.bucket_ref + bucket - 1];
+        uint32_t ref = t.hot[t.at.dir + (c0 & 0xFFFu)];
+        if (ref) {
             while (!(ref & REF_LEAF)) {
                 ++steps;
                 uint32_t child;
@@ -89,8 +87,8 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
                 } else {
                     const uint32_t* na = t.hot + t.at.nodes[0] + ref_index(ref) * 4;
                     const uint32_t* nb = t.hot + t.at.nodes[1] + ref_index(ref) * 4;
-                    const uint32_t f = (c0 & na[0]) ^ cb_rotl(c1 & na[1], (nb[0] >> 5) & 31u) ^ cb_rotl(c2 & na[2], (nb[0] >> 10) & 31u);
-                    child = nb[1] + ((f * na[3]) >> (nb[0] & 31u));
+                    const uint32_t f = (c0 & na[0]) ^ cb_rotl(c1 & na[1], nb[0]) ^ cb_rotl(c2 & na[2], nb[0] >> 5);
+                    child = nb[1] + ((f * na[3]) >> nb[2]);
                 }
                 ref = t.hot[t.at.children + child];
             }
