@@ -55,7 +55,8 @@ namespace cubit {
 enum : uint32_t {
     REF_LEAF = 1u << 31,    // leaf: [19:0] first class, [27:20] class count
     REF_NODE = 1u << 30,    // hash node: [19:0] node index
-    REF_BIT = 1u << 29,     // bit node: [19:0] first of two children, [26:20] bit of the word
+    REF_BIT = 1u << 29,     // bit node: [19:0] first of two children, [26:20] bit of the word (table compiler only:
+                            // bit nodes are folded into hash nodes before the table is finished)
 };
 CB_HD uint32_t ref_index(uint32_t r) { return r & 0xFFFFFu; }
 CB_HD uint32_t ref_count(uint32_t r) { return (r >> 20) & 0xFFu; }
@@ -352,19 +353,13 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
     *start = 0; *count = 0;
     uint32_t ref = HOT::w(t, t.at.dir + (c0 & 0xFFFu));
     if (ref == 0) return ST_NO_OPCODE;
+    // The table compiler folds every chain of bit nodes into a hash node over their bits, so
+    // the walk meets hash nodes only.
     while (!(ref & REF_LEAF)) {
-        uint32_t child;
-        if (ref & REF_BIT) {
-            const uint32_t bit = (ref >> 20) & 127u, w = bit >> 5;
-            const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
-            child = ref_index(ref) + (cb_shr_wrap(limb, bit) & 1u);
-        } else {
-            const uint32_t n = ref_index(ref) * 4u;
-            const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
-            const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.x >> 5);
-            child = b.y + ((f * a.w) >> b.z);
-        }
-        ref = HOT::w(t, t.at.children + child);
+        const uint32_t n = ref_index(ref) * 4u;
+        const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
+        const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.x >> 5);
+        ref = HOT::w(t, t.at.children + b.y + ((f * a.w) >> b.z));
     }
     *start = ref_index(ref);
     *count = ref_count(ref);

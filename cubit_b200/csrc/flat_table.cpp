@@ -334,6 +334,100 @@ struct TreeBuilder {
         return uint32_t(x) ^ cb_rotl(uint32_t(x >> 32), r1) ^ cb_rotl(uint32_t(x >> 64), r2);
     }
 
+    // A subtree of bit nodes becomes one hash node over its bits (at most kFlattenBits of them;
+    // deeper parts become hash nodes of their own): one step instead of a chain, and the kernel
+    // walks nodes of one kind only.  Every assignment of the bits is walked through the bit
+    // nodes here, so the new node reaches exactly the refs the chain reached.
+    static constexpr uint32_t kFlattenBits = 6;
+    uint32_t flatten_bits(uint32_t root) {
+        if (!(root & REF_BIT)) return root;
+        std::vector<uint32_t> bits;
+        {
+            std::vector<uint32_t> queue{root};
+            for (size_t q = 0; q < queue.size(); ++q) {
+                const uint32_t r = queue[q];
+                if (!(r & REF_BIT) || (r & REF_LEAF)) continue;
+                const uint32_t bit = (r >> 20) & 127u;
+                if (std::find(bits.begin(), bits.end(), bit) == bits.end()) {
+                    if (bits.size() >= kFlattenBits) continue;
+                    bits.push_back(bit);
+                }
+                queue.push_back(ft.children[ref_index(r)]);
+                queue.push_back(ft.children[ref_index(r) + 1]);
+            }
+        }
+        const uint32_t k = uint32_t(bits.size());
+        std::vector<u128> pattern(size_t(1) << k);
+        std::vector<uint32_t> target(size_t(1) << k);
+        u128 mask = 0;
+        for (uint32_t b : bits) mask |= (u128)1 << b;
+        for (uint32_t a = 0; a < (1u << k); ++a) {
+            u128 x = 0;
+            for (uint32_t j = 0; j < k; ++j)
+                if ((a >> j) & 1u) x |= (u128)1 << bits[j];
+            uint32_t r = root;
+            while ((r & REF_BIT) && !(r & REF_LEAF)) {
+                const uint32_t bit = (r >> 20) & 127u;
+                if (std::find(bits.begin(), bits.end(), bit) == bits.end()) break;
+                r = ft.children[ref_index(r) + uint32_t((x >> bit) & 1)];
+            }
+            pattern[a] = x;
+            target[a] = r;
+        }
+        uint64_t rng = 0x13198A2E03707344ull ^ root;
+        for (uint32_t extra = 0; extra < 4; ++extra) {
+            const uint32_t kk = k + extra;
+            for (uint32_t attempt = 0; attempt < 4000; ++attempt) {
+                rng = splitmix64(rng);
+                const uint32_t m = uint32_t(rng) | 1u;
+                const uint32_t a = (attempt / 64) % 32, b = (attempt / 7) % 32;
+                std::vector<char> seen(size_t(1) << kk, 0);
+                bool clash = false;
+                for (const u128& x : pattern) {
+                    const uint32_t h = kk ? (fold(x, a, b) * m) >> (32 - kk) : 0u;
+                    if (seen[h]) { clash = true; break; }
+                    seen[h] = 1;
+                }
+                if (clash) continue;
+                const uint32_t node = uint32_t(ft.nodes.size() / NR_WORDS);
+                ft.nodes.resize(ft.nodes.size() + NR_WORDS, 0);
+                const uint32_t child_base = uint32_t(ft.children.size());
+                if (child_base + (size_t(1) << kk) >= (1u << 20)) throw std::runtime_error("match tree too large");
+                ft.children.resize(ft.children.size() + (size_t(1) << kk), REF_LEAF);
+                for (size_t i = 0; i < pattern.size(); ++i)
+                    ft.children[child_base + ((fold(pattern[i], a, b) * m) >> (32 - kk))] = target[i];
+                uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
+                for (int q = 0; q < 3; ++q) n[NR_MASK + q] = uint32_t(mask >> (32 * q));
+                n[NR_MULT] = m;
+                n[NR_ROT] = a | (b << 5);
+                n[NR_CHILD] = child_base;
+                n[NR_SHIFT] = 32 - kk;
+                return REF_NODE | node;
+            }
+        }
+        throw std::runtime_error("no perfect hash for a bit-node subtree");
+    }
+    // Replaces every bit node reachable from `dir` (entries added on the way are visited too).
+    void flatten_all(std::vector<uint32_t>& dir) {
+        for (uint32_t& r : dir) r = flatten_bits(r);
+        for (size_t i = 0; i < ft.children.size(); ++i) {
+            const uint32_t r = ft.children[i];
+            if ((r & REF_BIT) && !(r & REF_LEAF) && reachable_as_child_of_node(i)) {
+                const uint32_t nr = flatten_bits(r);
+                ft.children[i] = nr;
+            }
+        }
+    }
+    // Child-table entries of hash nodes are the only ones the walk can still reach; entries of
+    // the two-entry tables of replaced bit nodes are dead.
+    bool reachable_as_child_of_node(size_t index) const {
+        for (size_t n = 0; n * NR_WORDS < ft.nodes.size(); ++n) {
+            const uint32_t base = ft.nodes[n * NR_WORDS + NR_CHILD], size = uint32_t(1) << (32 - ft.nodes[n * NR_WORDS + NR_SHIFT]);
+            if (index >= base && index < size_t(base) + size) return true;
+        }
+        return false;
+    }
+
     // Splits `vs` on the mask bits that all of them check (beyond `used`), then on single
     // bits that most of them check; recursion ends in leaves that no bit shrinks further.
     uint32_t build(const std::vector<uint32_t>& vs, u128 used, uint32_t depth) {
@@ -812,6 +906,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         ++ft.n_buckets;
         dir[b] = buckets[b].empty() ? uint32_t(REF_LEAF) : tb.build(buckets[b], 0xFFF, 0);
     }
+    tb.flatten_all(dir);
     ft.max_depth = tb.max_depth;
     if (ft.broad.empty()) ft.broad.assign(BR_WORDS, 0);
 
