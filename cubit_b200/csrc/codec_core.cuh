@@ -338,10 +338,14 @@ CB_HD uint32_t cb_lowmask(uint32_t nbits) {
 
 // <= 32 bits of cc starting at `src` (< 96).
 CB_HD uint32_t cb_extract(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t src, uint32_t nbits) {
-    const uint32_t w = src >> 5, sh = src & 31u;
-    const uint32_t lo = w == 0 ? c0 : (w == 1 ? c1 : c2);
-    const uint32_t hi = w == 0 ? c1 : (w == 1 ? c2 : 0u);
-    return cb_funnel_r(lo, hi, sh) & cb_lowmask(nbits);
+    const bool first = src < 32u, second = src < 64u;
+    const uint32_t lo = first ? c0 : (second ? c1 : c2);
+    const uint32_t hi = first ? c1 : (second ? c2 : 0u);
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_r(lo, hi, src) & cb_lowmask(nbits);   // the shift reads the low five bits of its amount
+#else
+    return cb_funnel_r(lo, hi, src & 31u) & cb_lowmask(nbits);
+#endif
 }
 
 // ---- variant selection -------------------------------------------------------------
