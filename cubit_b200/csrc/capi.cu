@@ -320,12 +320,46 @@ int fail(const cubit_ctx* ctx, int code, const std::string& msg) {
     return code;
 }
 
+// What an exported function returns when an exception reaches its outermost handler: nothing
+// may propagate into the caller's C frames.
+int translate_exception(const cubit_ctx* ctx) noexcept {
+    try {
+        try {
+            throw;
+        } catch (const TextError& e) {
+            return fail(ctx, CUBIT_ERR_TEXT, e.what());
+        } catch (const std::bad_alloc&) {
+            return fail(ctx, CUBIT_ERR_NOMEM, "out of host memory");
+        } catch (const std::exception& e) {
+            return fail(ctx, CUBIT_ERR_INVALID, e.what());
+        } catch (...) {
+            return fail(ctx, CUBIT_ERR_INVALID, "unknown failure");
+        }
+    } catch (...) {   // recording the message failed as well
+        return CUBIT_ERR_NOMEM;
+    }
+}
+
 #define CU_TRY(ctx, call)                                                                             \
     do {                                                                                              \
         cudaError_t e_ = (call);                                                                      \
         if (e_ != cudaSuccess)                                                                        \
             return fail(ctx, CUBIT_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));     \
     } while (0)
+
+// Frees what one device of a context holds; the device is made current first.
+void release_device(DeviceState* d) {
+    if (cudaSetDevice(d->device) != cudaSuccess) { cudaGetLastError(); return; }
+    cudaDeviceSynchronize();
+    for (void* p : d->table_allocs) cudaFree(p);
+    d->table_allocs.clear();
+    if (d->counters) cudaFree(d->counters);
+    if (d->stage) cudaFree(d->stage);
+    if (d->stream) cudaStreamDestroy(d->stream);
+    if (d->stream2) cudaStreamDestroy(d->stream2);
+    if (d->event) cudaEventDestroy(d->event);
+    d->counters = nullptr; d->stage = nullptr; d->stream = d->stream2 = nullptr; d->event = nullptr;
+}
 
 std::string bundled_table_path() {
     Dl_info info;
@@ -346,6 +380,35 @@ int upload(cubit_ctx* ctx, DeviceState* d, const std::vector<T>& host, const T**
     d->table_allocs.push_back(p);
     if (!host.empty()) CU_TRY(ctx, cudaMemcpy(p, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice));
     *out = (const T*)p;
+    return CUBIT_OK;
+}
+
+// Uploads the table to one device and creates its streams and counters.  Failures report
+// through the thread-local message, as the context does not exist yet for the caller.
+int init_device(const FlatTable& ft, DeviceState* d) {
+    cubit_ctx* c = nullptr;
+    CU_TRY(c, cudaSetDevice(d->device));
+    CU_TRY(c, cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, d->device));
+    const uint32_t* blob = nullptr;
+    const int rc = upload(c, d, ft.blob, &blob);
+    if (rc) return rc;
+    d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
+    d->hot_bytes = ft.at.hot_words * 4;
+    d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
+    int optin = 0;
+    CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
+    d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
+    if (d->shared_ok) {
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+    }
+    CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
+    for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
+    CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+    CU_TRY(c, cudaStreamCreateWithFlags(&d->stream2, cudaStreamNonBlocking));
+    CU_TRY(c, cudaEventCreateWithFlags(&d->event, cudaEventDisableTiming));
     return CUBIT_OK;
 }
 
@@ -501,6 +564,11 @@ int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint
     if (e == cudaSuccess) e = cudaStreamSynchronize(streams[1]);
     if (e == cudaSuccess && dc) e = cudaMemcpyAsync(host, dc, sizeof host, cudaMemcpyDeviceToHost, streams[0]);
     if (e == cudaSuccess) e = cudaStreamSynchronize(streams[0]);
+    if (e != cudaSuccess) {   // nothing may still be using the staging area or the counter slot
+        cudaStreamSynchronize(streams[0]);
+        cudaStreamSynchronize(streams[1]);
+        cudaGetLastError();
+    }
     if (slot >= 0) give_counter_slot(d, slot);
     if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string("host decode: ") + cudaGetErrorString(e));
     if (counts) add_counts(counts, host);
@@ -567,6 +635,10 @@ int for_each_device(cubit_ctx* ctx, cubit_counts* counts, Fn fn) {
     auto body = [&](size_t k) {
         rcs[k] = fn(k, counts ? &partial[k] : nullptr);
         if (rcs[k]) messages[k] = cubit_last_error(ctx);
+        if (g > 1) {   // a worker thread ends here: its message slot goes with it
+            std::lock_guard<std::mutex> lock(ctx->err_mu);
+            ctx->errors.erase(std::this_thread::get_id());
+        }
     };
     if (g == 1) {
         body(0);
@@ -617,7 +689,7 @@ int get_synth_view(cubit_ctx* ctx, DeviceState* d, uint32_t mix, uint64_t seed, 
 
 // ---- exported: context ------------------------------------------------------------------------
 
-extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int n_devices, cubit_ctx** out) {
+extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int n_devices, cubit_ctx** out) try {
     if (!out || n_devices < 0 || (n_devices > 0 && !devices)) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
     *out = nullptr;
     std::unique_ptr<cubit_ctx> ctx(new cubit_ctx);
@@ -645,47 +717,23 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
     for (int k = 0; k < n_devices; ++k) {
         std::unique_ptr<DeviceState> d(new DeviceState);
         d->device = devices[k];
-        cubit_ctx* c = nullptr;   // failures during creation report through the thread-local message
-        CU_TRY(c, cudaSetDevice(d->device));
-        CU_TRY(c, cudaDeviceGetAttribute(&d->sm_count, cudaDevAttrMultiProcessorCount, d->device));
-        const uint32_t* blob = nullptr;
-        int rc = upload(c, d.get(), ft.blob, &blob);
-        if (rc) return rc;
-        d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
-        d->hot_bytes = ft.at.hot_words * 4;
-        d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
-        int optin = 0;
-        CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
-        d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
-        if (d->shared_ok) {
-            CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-            CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
-            CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-            CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        const int rc = init_device(ft, d.get());
+        if (rc) {   // give back what this and the earlier devices already hold
+            release_device(d.get());
+            for (auto& made : ctx->devs) release_device(made.get());
+            return rc;
         }
-        CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
-        for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
-        CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
-        CU_TRY(c, cudaStreamCreateWithFlags(&d->stream2, cudaStreamNonBlocking));
-        CU_TRY(c, cudaEventCreateWithFlags(&d->event, cudaEventDisableTiming));
         ctx->devs.push_back(std::move(d));
     }
     *out = ctx.release();
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(nullptr);
 }
 
 extern "C" void cubit_ctx_destroy(cubit_ctx* ctx) {
     if (!ctx) return;
-    for (auto& d : ctx->devs) {
-        cudaSetDevice(d->device);
-        cudaDeviceSynchronize();
-        for (void* p : d->table_allocs) cudaFree(p);
-        if (d->counters) cudaFree(d->counters);
-        if (d->stage) cudaFree(d->stage);
-        if (d->stream) cudaStreamDestroy(d->stream);
-        if (d->stream2) cudaStreamDestroy(d->stream2);
-        if (d->event) cudaEventDestroy(d->event);
-    }
+    for (auto& d : ctx->devs) release_device(d.get());
     delete ctx;
 }
 
@@ -696,14 +744,16 @@ extern "C" const char* cubit_last_error(const cubit_ctx* ctx) {
     return c->errors[std::this_thread::get_id()].c_str();
 }
 
-extern "C" int cubit_table_info(const cubit_ctx* ctx, uint32_t* n_keys, uint32_t* n_groups) {
+extern "C" int cubit_table_info(const cubit_ctx* ctx, uint32_t* n_keys, uint32_t* n_groups) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (n_keys) *n_keys = (uint32_t)ctx->table.num_keys();
     if (n_groups) *n_groups = (uint32_t)ctx->table.num_groups();
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
-extern "C" int cubit_variant_lookup(const cubit_ctx* ctx, uint32_t variant, cubit_variant_info* out) {
+extern "C" int cubit_variant_lookup(const cubit_ctx* ctx, uint32_t variant, cubit_variant_info* out) try {
     if (!ctx || !out) return CUBIT_ERR_INVALID;
     if (variant >= ctx->flat.meta.size()) return fail(ctx, CUBIT_ERR_NOT_FOUND, "variant id out of range");
     const VariantMeta& m = ctx->flat.meta[variant];
@@ -713,18 +763,22 @@ extern "C" int cubit_variant_lookup(const cubit_ctx* ctx, uint32_t variant, cubi
     out->n_fields = (uint32_t)m.fields.size();
     out->fields = ctx->field_infos[variant].data();
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
-extern "C" int cubit_variant_find(const cubit_ctx* ctx, const char* key, const char* mod_group, uint32_t* variant) {
+extern "C" int cubit_variant_find(const cubit_ctx* ctx, const char* key, const char* mod_group, uint32_t* variant) try {
     if (!ctx || !key || !mod_group || !variant) return CUBIT_ERR_INVALID;
     auto it = ctx->by_name.find({key, mod_group});
     if (it == ctx->by_name.end()) return fail(ctx, CUBIT_ERR_NOT_FOUND, std::string("no table entry ") + key + "::" + mod_group);
     *variant = it->second;
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_key_name(const cubit_ctx* ctx, uint32_t key_id, const char** name, uint32_t* first_variant,
-                              uint32_t* n_variants) {
+                              uint32_t* n_variants) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (key_id >= ctx->table.keys.size()) return fail(ctx, CUBIT_ERR_NOT_FOUND, "key id out of range");
     const IsaKey& k = ctx->table.keys[key_id];
@@ -732,26 +786,32 @@ extern "C" int cubit_key_name(const cubit_ctx* ctx, uint32_t key_id, const char*
     if (first_variant) *first_variant = k.first_variant;
     if (n_variants) *n_variants = k.n_variants;
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
-extern "C" int cubit_host_alloc(cubit_ctx* ctx, uint64_t bytes, void** out) {
+extern "C" int cubit_host_alloc(cubit_ctx* ctx, uint64_t bytes, void** out) try {
     if (!ctx || !out) return CUBIT_ERR_INVALID;
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "context has no CUDA device");
     CU_TRY(ctx, cudaSetDevice(ctx->devs[0]->device));
     CU_TRY(ctx, cudaHostAlloc(out, std::max<uint64_t>(bytes, 1), cudaHostAllocPortable));
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
-extern "C" int cubit_host_free(cubit_ctx* ctx, void* p) {
+extern "C" int cubit_host_free(cubit_ctx* ctx, void* p) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (p) CU_TRY(ctx, cudaFreeHost(p));
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // ---- exported: batch codec ----------------------------------------------------------------------
 
 extern "C" int cubit_decode_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint16_t* form, uint32_t* slots,
-                                  uint32_t* ctrl, cubit_counts* counts, int mem_kind, void* stream) {
+                                  uint32_t* ctrl, cubit_counts* counts, int mem_kind, void* stream) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (counts) memset(counts, 0, sizeof *counts);
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "decode needs a CUDA device; this context has none");
@@ -775,10 +835,12 @@ extern "C" int cubit_decode_batch(cubit_ctx* ctx, const void* words, uint64_t n,
         if (b == e) return (int)CUBIT_OK;
         return decode_host_range(ctx, ctx->devs[k].get(), (const uint8_t*)words, n, b, e, form, slots, ctrl, part);
     });
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_encode_batch(cubit_ctx* ctx, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl,
-                                  uint64_t n, void* words, int mem_kind, void* stream) {
+                                  uint64_t n, void* words, int mem_kind, void* stream) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "encode needs a CUDA device; this context has none");
     if (n == 0) return CUBIT_OK;
@@ -801,10 +863,12 @@ extern "C" int cubit_encode_batch(cubit_ctx* ctx, const uint16_t* form, const ui
         if (b == e) return (int)CUBIT_OK;
         return encode_host_range(ctx, ctx->devs[k].get(), form, slots, ctrl, n, b, e, (uint8_t*)words);
     });
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_roundtrip_batch(cubit_ctx* ctx, const void* words, uint64_t n, uint8_t* status,
-                                     cubit_counts* counts, int mem_kind, void* stream) {
+                                     cubit_counts* counts, int mem_kind, void* stream) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (counts) memset(counts, 0, sizeof *counts);
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "roundtrip needs a CUDA device; this context has none");
@@ -828,11 +892,13 @@ extern "C" int cubit_roundtrip_batch(cubit_ctx* ctx, const void* words, uint64_t
         if (b == e) return (int)CUBIT_OK;
         return roundtrip_host_range(ctx, ctx->devs[k].get(), (const uint8_t*)words, b, e, status, part);
     });
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, uint32_t noise_ppm, uint64_t first,
                                  uint64_t n, void* words, uint16_t* form, uint32_t* slots, uint32_t* ctrl, int mem_kind,
-                                 void* stream) {
+                                 void* stream) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "the stream generator needs a CUDA device");
     if (n == 0) return CUBIT_OK;
@@ -880,11 +946,13 @@ extern "C" int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, ui
         CU_TRY(ctx, cudaStreamSynchronize(d->stream));
     }
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // Host-buffer decode of a small batch that allocates nothing: see include/cubit_b200.h.
 extern "C" int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const void* words, uint64_t n, uint16_t* form,
-                                         uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
+                                         uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (counts) memset(counts, 0, sizeof *counts);
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "decode needs a CUDA device; this context has none");
@@ -895,6 +963,7 @@ extern "C" int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const 
     if (n == 0) return CUBIT_OK;
     if (!words || !form || !slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
     DeviceState* d = ctx->devs[(size_t)device_slot].get();
+    std::lock_guard<std::mutex> lock(d->stage_mu);   // one user of the scratch array and of the stream at a time
     CU_TRY(ctx, cudaSetDevice(d->device));
     {
         // One-time set-up per device, with that device current: the symbol's address there.
@@ -922,11 +991,13 @@ extern "C" int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const 
     CU_TRY(ctx, cudaStreamSynchronize(d->stream));
     if (counts) add_counts(counts, host_counts);
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // ---- exported: cubin ----------------------------------------------------------------------------
 
-extern "C" int cubit_elf_parse(const void* bytes, uint64_t len, cubit_elf** out) {
+extern "C" int cubit_elf_parse(const void* bytes, uint64_t len, cubit_elf** out) try {
     if (!bytes || !out) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
     *out = nullptr;
     std::unique_ptr<cubit_elf> e(new cubit_elf);
@@ -939,21 +1010,25 @@ extern "C" int cubit_elf_parse(const void* bytes, uint64_t len, cubit_elf** out)
     }
     *out = e.release();
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(nullptr);
 }
 
 extern "C" void cubit_elf_free(cubit_elf* elf) { delete elf; }
 
 extern "C" uint32_t cubit_elf_num_text(const cubit_elf* elf) { return elf ? (uint32_t)elf->text.size() : 0; }
 
-extern "C" int cubit_elf_text(const cubit_elf* elf, uint32_t index, const char** name, uint64_t* offset, uint64_t* size) {
+extern "C" int cubit_elf_text(const cubit_elf* elf, uint32_t index, const char** name, uint64_t* offset, uint64_t* size) try {
     if (!elf || index >= elf->text.size()) return fail(nullptr, CUBIT_ERR_INVALID, "text section index out of range");
     if (name) *name = elf->text[index].name.c_str();
     if (offset) *offset = elf->text[index].offset;
     if (size) *size = elf->text[index].size;
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(nullptr);
 }
 
-extern "C" int cubit_elf_find(const cubit_elf* elf, const char* kernel_name, uint32_t* index) {
+extern "C" int cubit_elf_find(const cubit_elf* elf, const char* kernel_name, uint32_t* index) try {
     if (!elf || !kernel_name || !index) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
     for (size_t i = 0; i < elf->text.size(); ++i)
         if (elf->text[i].name.find(kernel_name) != std::string::npos) {
@@ -963,11 +1038,13 @@ extern "C" int cubit_elf_find(const cubit_elf* elf, const char* kernel_name, uin
     std::string names;
     for (const TextSection& t : elf->text) names += (names.empty() ? "\"" : ", \"") + t.name + "\"";
     return fail(nullptr, CUBIT_ERR_NOT_FOUND, std::string("kernel '") + kernel_name + "' not found. Available: [" + names + "]");
+} catch (...) {
+    return translate_exception(nullptr);
 }
 
 extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indices, uint32_t n_sections,
                                 uint64_t* word_start, uint64_t capacity, uint16_t* form, uint32_t* slots,
-                                uint32_t* ctrl, void* raw_words, cubit_counts* counts) {
+                                uint32_t* ctrl, void* raw_words, cubit_counts* counts) try {
     if (!ctx || !elf || !word_start) return fail(ctx, CUBIT_ERR_INVALID, "bad argument");
     if (counts) memset(counts, 0, sizeof *counts);
     if (!indices) n_sections = (uint32_t)elf->text.size();
@@ -1033,11 +1110,13 @@ extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint
         CU_TRY(ctx, cudaStreamSynchronize(d->stream));
         return (int)CUBIT_OK;
     });
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, const uint32_t* indices, uint32_t n_sections,
                                        cubit_kernel_meta* meta, uint32_t* exit_offsets, uint64_t exit_capacity,
-                                       uint64_t* n_exits) {
+                                       uint64_t* n_exits) try {
     if (!ctx || !elf || !meta || !n_exits) return fail(ctx, CUBIT_ERR_INVALID, "bad argument");
     *n_exits = 0;
     if (ctx->devs.empty()) return fail(ctx, CUBIT_ERR_NO_DEVICE, "metadata inference needs a CUDA device; this context has none");
@@ -1108,10 +1187,12 @@ extern "C" int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, con
     *n_exits = ne;
     if (exit_offsets && ne > exit_capacity) return fail(ctx, CUBIT_ERR_INVALID, "exit_offsets capacity below the number of EXIT instructions");
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_elf_build(const char* const* names, const void* const* code, const uint64_t* code_bytes,
-                               uint32_t n_kernels, void* out, uint64_t capacity, uint64_t* out_len) {
+                               uint32_t n_kernels, void* out, uint64_t capacity, uint64_t* out_len) try {
     if (!out_len || (n_kernels && (!names || !code || !code_bytes))) return fail(nullptr, CUBIT_ERR_INVALID, "bad argument");
     std::vector<BuildKernel> ks;
     for (uint32_t k = 0; k < n_kernels; ++k) ks.push_back(BuildKernel{names[k], (const uint8_t*)code[k], code_bytes[k]});
@@ -1121,6 +1202,8 @@ extern "C" int cubit_elf_build(const char* const* names, const void* const* code
         return fail(nullptr, CUBIT_ERR_ELF, e.what());
     }
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(nullptr);
 }
 
 // ---- SASS text ---------------------------------------------------------------------------
@@ -1245,7 +1328,7 @@ void json_escape(const std::string& s, std::string* out) {
 
 extern "C" int cubit_text_lower(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
                                 uint16_t* form, uint32_t* slots, uint32_t* ctrl, void* clear, void* set,
-                                uint64_t* n_out) {
+                                uint64_t* n_out) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!text || !n_out) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     if (mode != CUBIT_TEXT_ONE && mode != CUBIT_TEXT_PROGRAM) return fail(ctx, CUBIT_ERR_INVALID, "unknown text mode");
@@ -1268,10 +1351,12 @@ extern "C" int cubit_text_lower(cubit_ctx* ctx, const char* text, uint32_t base_
         memcpy((uint8_t*)set + i * 16, &b.set[i], 16);
     }
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_text_encode(cubit_ctx* ctx, const char* text, uint32_t base_addr, int mode, uint64_t capacity,
-                                 void* words, uint64_t* n_out) {
+                                 void* words, uint64_t* n_out) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!text || !n_out) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     if (mode != CUBIT_TEXT_ONE && mode != CUBIT_TEXT_PROGRAM) return fail(ctx, CUBIT_ERR_INVALID, "unknown text mode");
@@ -1298,10 +1383,12 @@ extern "C" int cubit_text_encode(cubit_ctx* ctx, const char* text, uint32_t base
         memcpy((uint8_t*)words + i * 16, &w, 16);
     }
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_text_parse(cubit_ctx* ctx, const char* line, uint32_t addr, char* json, uint64_t capacity,
-                                uint64_t* needed) {
+                                uint64_t* needed) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!line || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     TextInstruction insn;
@@ -1369,6 +1456,8 @@ extern "C" int cubit_text_parse(cubit_ctx* ctx, const char* line, uint32_t addr,
     *needed = j.size() + 1;
     if (json && capacity >= j.size() + 1) memcpy(json, j.c_str(), j.size() + 1);
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 namespace {
@@ -1442,7 +1531,7 @@ std::string print_word(const cubit_ctx* ctx, const uint8_t* words, uint64_t i, u
 
 extern "C" int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, uint32_t base_addr, const uint16_t* form,
                                 const uint32_t* slots, const uint32_t* ctrl, char* out, uint64_t capacity,
-                                uint64_t* needed) {
+                                uint64_t* needed) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!needed || (n && !words)) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     std::vector<uint16_t> f;
@@ -1464,6 +1553,8 @@ extern "C" int cubit_text_print(cubit_ctx* ctx, const void* words, uint64_t n, u
     *needed = text.size() + 1;
     if (out && capacity >= text.size() + 1) memcpy(out, text.c_str(), text.size() + 1);
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // ---- listings ------------------------------------------------------------------------------
@@ -1597,7 +1688,7 @@ KernelInfo kernel_info(const cubit_elf* elf, const std::vector<ElfSection>& sect
 }  // namespace
 
 extern "C" int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const char* only_kernel, int frozen, char* out,
-                                 uint64_t capacity, uint64_t* needed, uint64_t* n_raw) {
+                                 uint64_t capacity, uint64_t* needed, uint64_t* n_raw) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!elf || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     if (n_raw) *n_raw = 0;
@@ -1771,12 +1862,14 @@ extern "C" int cubit_disassemble(cubit_ctx* ctx, const cubit_elf* elf, const cha
     *needed = listing.size() + 1;
     if (out && capacity >= listing.size() + 1) memcpy(out, listing.c_str(), listing.size() + 1);
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // ---- plain listing -> code -------------------------------------------------------------------
 
 extern "C" int cubit_listing_assemble(cubit_ctx* ctx, const char* listing, const char* kernel, void* code,
-                                      uint64_t capacity, uint64_t* needed, uint64_t* n_failed) {
+                                      uint64_t capacity, uint64_t* needed, uint64_t* n_failed) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!listing || !kernel || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     if (n_failed) *n_failed = 0;
@@ -1942,12 +2035,14 @@ extern "C" int cubit_listing_assemble(cubit_ctx* ctx, const char* listing, const
         if (l.raw) memcpy(out + l.addr, &l.word, 16);
     if (n_failed) *n_failed = failed;
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 // ---- cubin rewriting -------------------------------------------------------------------------
 
 extern "C" int cubit_patch_elf(cubit_ctx* ctx, const cubit_elf* elf, void* out, uint64_t capacity, uint64_t* needed,
-                               cubit_patch_stats* stats) {
+                               cubit_patch_stats* stats) try {
     if (!ctx) return CUBIT_ERR_INVALID;
     if (!elf || !needed) return fail(ctx, CUBIT_ERR_INVALID, "null argument");
     cubit_patch_stats st;
@@ -2012,10 +2107,12 @@ extern "C" int cubit_patch_elf(cubit_ctx* ctx, const cubit_elf* elf, void* out, 
     st.n_kept = total - m;
     if (stats) *stats = st;
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(ctx);
 }
 
 extern "C" int cubit_elf_patch_text(const cubit_elf* elf, uint32_t index, const void* code, uint64_t code_len, void* out,
-                                    uint64_t capacity, uint64_t* needed) {
+                                    uint64_t capacity, uint64_t* needed) try {
     if (!elf || !needed || (code_len && !code)) return fail(nullptr, CUBIT_ERR_INVALID, "null argument");
     std::vector<uint8_t> file;
     try {
@@ -2026,4 +2123,6 @@ extern "C" int cubit_elf_patch_text(const cubit_elf* elf, uint32_t index, const 
     *needed = file.size();
     if (out && capacity >= file.size()) memcpy(out, file.data(), file.size());
     return CUBIT_OK;
+} catch (...) {
+    return translate_exception(nullptr);
 }

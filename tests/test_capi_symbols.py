@@ -46,6 +46,20 @@ def test_bad_arguments_return_codes_not_crashes():
     assert lib.cubit_elf_num_text(None) == 0
 
 
+def test_context_creation_failure_returns_a_code_and_a_message(monkeypatch):
+    """A device that cannot be opened and a table that cannot be read: an error code, a message
+    under cubit_last_error(NULL), no context, and nothing thrown through the C frames."""
+    lib = _native.load_library()
+    ctx = C.c_void_p()
+    import torch
+    if not torch.cuda.is_available():
+        devices = (C.c_int * 1)(0)
+        assert lib.cubit_ctx_create(None, devices, 1, C.byref(ctx)) == -3 and not ctx.value
+        assert b"cuda" in lib.cubit_last_error(None).lower()
+    assert lib.cubit_ctx_create(b"/nonexistent/sm120.json", None, 0, C.byref(ctx)) == -2 and not ctx.value
+    assert b"/nonexistent/sm120.json" in lib.cubit_last_error(None)
+
+
 def test_text_layer_entry_points_say_what_is_missing():
     with pytest.raises(NotImplementedError, match="scheduling pass"):
         cubit_b200.asm("NOP")
