@@ -194,6 +194,55 @@ def test_device_pointer_path(codec, oracle):
     assert rcounts["n_exact"] == int((ostatus == 0).sum())
 
 
+def test_one_context_from_several_host_threads(codec, oracle):
+    """Four host threads share the context: two decode device buffers on streams of their own
+    (counted launches, so they also share the counter slots), two go through the host-buffer
+    path (which shares the staging area).  ctypes releases the GIL during the calls."""
+    import threading
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda", 0)
+    n = 300001
+    batches = [oracle.synth(MIX_ZIPF, 20 + k, n, noise_ppm=5000, records=False) for k in range(4)]
+    want = [oracle.decode_batch(b, threads=T) for b in batches]
+    got, errors = [None] * 4, []
+
+    def device_worker(k):
+        try:
+            torch.cuda.set_device(dev)
+            s = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(s):
+                dw = torch.from_numpy(batches[k].reshape(-1)).to(dev, non_blocking=False)
+                form = torch.empty(n, dtype=torch.int16, device=dev)
+                slots = torch.empty(8 * n, dtype=torch.int32, device=dev)
+                ctrl = torch.empty(n, dtype=torch.int32, device=dev)
+                for _ in range(5):
+                    c = codec.decode_device(dw.data_ptr(), n, form.data_ptr(), slots.data_ptr(), ctrl.data_ptr(),
+                                            stream=s.cuda_stream, want_counts=True)
+                    assert c["n_decoded"] + c["n_rejected"] == n
+                s.synchronize()
+                got[k] = (form.cpu().numpy().view(np.uint16), slots.cpu().numpy().view(np.uint32).reshape(8, n),
+                          ctrl.cpu().numpy().view(np.uint32))
+        except BaseException as e:   # noqa: BLE001 - reported by the main thread
+            errors.append(e)
+
+    def host_worker(k):
+        try:
+            for _ in range(3):
+                got[k] = codec.decode_batch(batches[k])[:3]
+        except BaseException as e:   # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=device_worker, args=(0,)), threading.Thread(target=device_worker, args=(1,)),
+               threading.Thread(target=host_worker, args=(2,)), threading.Thread(target=host_worker, args=(3,))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for k in range(4):
+        assert_records_equal(got[k], want[k])
+
+
 def test_stream_ranges_compose(codec):
     """Any range of a stream can be generated on its own: shards of one stream agree with the whole."""
     whole = codec.synth(MIX_ZIPF, 9, 5000, noise_ppm=10000)
@@ -238,6 +287,34 @@ def test_full_size_properties(codec, oracle):
     assert (form[idx].cpu().numpy().view(np.uint16) == oform).all()
     assert (slots.view(8, n)[:, idx].cpu().numpy().view(np.uint32) == oslots).all()
     assert (ctrl[idx].cpu().numpy().view(np.uint32) == octrl).all()
+    assert (status[idx].cpu().numpy() == oracle.roundtrip_batch(sample, threads=T)).all()
+
+
+def test_roundtrip_at_the_largest_configuration(codec, oracle):
+    """256 Mi words (4 GiB) with 1 % raw random words in one fused roundtrip launch: the status
+    classes partition the batch, a second launch over a sub-range reproduces the first one's
+    bytes, and every 256th word has the oracle's status."""
+    torch = pytest.importorskip("torch")
+    n = 256 * 1024 * 1024
+    dev = torch.device("cuda", 0)
+    if torch.cuda.mem_get_info(dev)[0] < 6 * (1 << 30):
+        pytest.skip("needs 6 GiB of free device memory")
+    words = torch.empty(n * 16, dtype=torch.uint8, device=dev)
+    status = torch.empty(n, dtype=torch.uint8, device=dev)
+    codec.synth_device(MIX_ZIPF, 1, n, words_ptr=words.data_ptr(), noise_ppm=10000)
+    rc = codec.roundtrip_device(words.data_ptr(), n, status.data_ptr(), want_counts=True)
+    torch.cuda.synchronize()
+    assert rc["n_exact"] + rc["n_mismatch"] + rc["n_rejected"] == n
+    hist = torch.bincount(status.to(torch.int64), minlength=3)
+    assert hist.tolist() == [rc["n_exact"], rc["n_mismatch"], rc["n_rejected"]]
+    assert rc["n_rejected"] >= n // 200          # the raw random words are nearly all rejected
+    begin, m = 3 * n // 4 + 5, 1 << 20            # an unaligned-by-word sub-range, as another launch
+    again = torch.empty(m, dtype=torch.uint8, device=dev)
+    codec.roundtrip_device(words.data_ptr() + begin * 16, m, again.data_ptr())
+    torch.cuda.synchronize()
+    assert bool((again == status[begin:begin + m]).all())
+    idx = torch.arange(0, n, 256, device=dev)
+    sample = words.view(n, 16)[idx].cpu().numpy()
     assert (status[idx].cpu().numpy() == oracle.roundtrip_batch(sample, threads=T)).all()
 
 
