@@ -43,6 +43,7 @@ struct FlatTable {
     std::vector<uint32_t> enc;       // ER_WORDS per distinct field layout: the encoder's view of `ext`
     std::vector<uint32_t> var;       // VR_WORDS per variant
     std::vector<uint32_t> gfields;
+    std::vector<uint32_t> gindex;    // per variant: first generator field | count << 24
     std::vector<uint32_t> metaf;     // MF_WORDS per variant
     std::vector<uint32_t> rt;        // 8 per variant: roundtrip constants
     std::vector<VariantMeta> meta;
