@@ -91,6 +91,8 @@ enum : uint32_t {           // CR_INFO
     CI_HAS_BROAD = 1u << 12,
     CI_MEMBERS_POS = 13,          // 8 bits
     CI_TIE_WITHIN = 1u << 21,     // best member shares its rank tuple with another member
+    CI_RELEVANT_POS = 22,         // 10 bits, the same in every class of a leaf: which of the leaf's first ten classes
+    CI_RELEVANT_BITS = 10,        // have a broad record that still matters when some class matched strictly
 };
 enum { BR_WORDS = 8 };      // broad record (hot): mask[3], base[3], pad
 // Per-flag table (cold) of a class with several members: for each of the 16 choice flags the
@@ -487,7 +489,7 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         // branch would be taken by some lane of the warp in nearly every iteration).  Which
         // classes of the leaf have a broad record is a constant of the leaf, kept in the upper
         // half of every class's flag word for leaves of at most 16 classes.
-        uint32_t strict = 0, broad = 0, pending = 0, leaf_broad = 0;
+        uint32_t strict = 0, broad = 0, pending = 0, leaf_broad = 0, leaf_info = 0;
         {
             uint32_t bit = 1u;
 #pragma unroll 2
@@ -497,10 +499,15 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
                 strict |= hit ? bit : 0u;
                 any |= hit ? b.w : 0u;
                 leaf_broad = b.w;
+                leaf_info = b.z;
             }
         }
         if (count <= 16) {
-            pending = (leaf_broad >> 16) & ~strict;
+            // With a strict match, only the broad records the table compiler marked can still
+            // change the outcome (classes beyond the marked ten always count).
+            leaf_broad >>= 16;
+            const uint32_t relevant = (leaf_info >> CI_RELEVANT_POS) | ~((1u << CI_RELEVANT_BITS) - 1u);
+            pending = leaf_broad & ~strict & (strict ? relevant : 0xFFFFFFFFu);
         } else {
             for (uint32_t i = 0; i < chunk; ++i)
                 if (!((strict >> i) & 1u) && (HOT::w(t, t.at.classes[1] + (r0 + i) * 4u + 2u) & CI_HAS_BROAD)) pending |= 1u << i;

@@ -286,7 +286,31 @@ struct TreeBuilder {
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
             leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = (info & CI_TIE_WITHIN) ? 1u : 0u;
         }
-        for (size_t ci = 0; ci < order.size(); ++ci) ft.classes[(size_t(first_class) + ci) * CR_WORDS + CR_ANY_FLAGS] |= leaf_broad16 << 16;
+        // Broad records that cannot change the outcome once some class matches strictly: every
+        // strictly matchable class of the leaf has a non-negative score (so a strict match is on
+        // top whatever else matches), and the class's choice flags are carried by the best member
+        // of each of them (so its flags add nothing to the union the rules look at, and the
+        // second pass, which asks for a flag the top candidate lacks, would pass it over).
+        uint32_t leaf_relevant = 0;
+        {
+            uint32_t common = 0xFFFFu;
+            bool nonneg = true;
+            for (size_t ci = 0; ci < order.size(); ++ci) {
+                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
+                if (!st[groups[order[ci]][0]].s_ok) continue;
+                common &= rec[CR_FIRST_FLAGS];
+                if (rec[CR_KEY] >> 31) nonneg = false;
+            }
+            for (size_t ci = 0; ci < order.size() && ci < CI_RELEVANT_BITS; ++ci) {
+                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
+                if ((rec[CR_INFO] & CI_HAS_BROAD) && (!nonneg || (rec[CR_ANY_FLAGS] & 0xFFFFu & ~common))) leaf_relevant |= 1u << ci;
+            }
+        }
+        for (size_t ci = 0; ci < order.size(); ++ci) {
+            uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
+            rec[CR_ANY_FLAGS] |= leaf_broad16 << 16;
+            rec[CR_INFO] |= leaf_relevant << CI_RELEVANT_POS;
+        }
         // Ranking memo: when some pair of the leaf is not settled by position and the word-dependent
         // part of every strictly matchable class reads only the guard nibble, run the ranking loop
         // of the kernel here for every (guard nibble, set of strict matches).
