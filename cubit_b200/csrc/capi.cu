@@ -85,9 +85,10 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
     const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
-    uint32_t tally[3] = {0, 0, 0};
+    uint32_t n_ok = 0, n_tie = 0;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i < n; i += step) {
         const uint4 w = __ldcs(words + i);
         uint32_t f, c, s[8];
         decode_word<HOT>(t, w.x, w.y, w.z, w.w, &f, s, &c);
@@ -95,10 +96,13 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t
 #pragma unroll
         for (int k = 0; k < 8; ++k) __stcs(slots + (uint64_t)k * slot_stride + i, s[k]);
         __stcs(ctrl + i, c);
-        const bool ok = (c >> 30) == ST_OK;
-        tally[0] += ok; tally[1] += !ok; tally[2] += (c >> 28) & 1u;
+        n_ok += (c >> 30) == ST_OK;
+        n_tie += (c >> 28) & 1u;
     }
     if (counters) {
+        // Rejected words are the rest of this thread's share of the batch.
+        const uint32_t seen = first < n ? (uint32_t)((n - first + step - 1) / step) : 0u;
+        const uint32_t tally[3] = {n_ok, seen - n_ok, n_tie};
         const int which[3] = {CNT_DECODED, CNT_REJECTED, CNT_TIE};
         block_tally(tally, which, counters);
     }
@@ -172,15 +176,18 @@ __global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockSh
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
     const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
-    uint32_t tally[3] = {0, 0, 0};
+    uint32_t n_exact = 0, n_rejected = 0;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint64_t i = first; i < n; i += step) {
         const uint4 w = __ldcs(words + i);
         const uint32_t st = roundtrip_word<HOT>(t, w.x, w.y, w.z, w.w);
         __stcs(status + i, (uint8_t)st);
-        tally[0] += st == RT_EXACT; tally[1] += st == RT_MISMATCH; tally[2] += st == RT_REJECTED;
+        n_exact += st == RT_EXACT; n_rejected += st == RT_REJECTED;
     }
     if (counters) {
+        const uint32_t seen = first < n ? (uint32_t)((n - first + step - 1) / step) : 0u;
+        const uint32_t tally[3] = {n_exact, seen - n_exact - n_rejected, n_rejected};
         const int which[3] = {CNT_EXACT, CNT_MISMATCH, CNT_REJECTED};
         block_tally(tally, which, counters);
     }
