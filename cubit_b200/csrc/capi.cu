@@ -60,6 +60,19 @@ __device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t, ui
     v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem) - begin * 4u;
     return v;
 }
+// The roundtrip kernel's two ranges: blob words [0, rt_cut), then the roundtrip constants.
+template <>
+__device__ __forceinline__ FlatView stage_table<HotSharedRT>(const FlatView& t, uint32_t, uint32_t) {
+    const uint4* src = reinterpret_cast<const uint4*>(t.cold);
+    const uint32_t quads_a = t.at.classes[3] / 4, first_b = t.at.rt[0] / 4, quads_b = (t.at.total_words - t.at.rt[0]) / 4;
+    for (uint32_t i = threadIdx.x; i < quads_a; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
+    for (uint32_t i = threadIdx.x; i < quads_b; i += blockDim.x) g_table_smem[quads_a + i] = __ldg(src + first_b + i);
+    __syncthreads();
+    FlatView v = t;
+    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem);
+    v.rt_s = v.hot_s + t.at.classes[3] * 4u - t.at.rt[0] * 4u;
+    return v;
+}
 
 // Adds per-thread tallies into the launch's counters: warp reduce, then one shared atomic
 // per warp, then one global atomic per block.
@@ -172,7 +185,7 @@ encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __
 }
 
 template <class HOT>
-__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
     const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
@@ -273,6 +286,8 @@ struct DeviceState {
     int device = -1;
     int sm_count = 0;
     bool shared_ok = false;   // the hot part of the table fits the opt-in shared memory of this device
+    bool rt_shared_ok = false;   // so do the roundtrip kernel's two ranges (selection tables + roundtrip constants)
+    uint32_t rt_bytes = 0;
     uint32_t hot_bytes = 0;   // decode window of the table
     uint32_t enc_bytes = 0;   // encode window
     FlatView view{};
@@ -399,7 +414,7 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     const uint32_t* blob = nullptr;
     const int rc = upload(c, d, ft.blob, &blob);
     if (rc) return rc;
-    d->view.hot = blob; d->view.cold = blob; d->view.hot_s = 0; d->view.at = ft.at;
+    d->view.cold = blob; d->view.hot_s = 0; d->view.rt_s = 0; d->view.at = ft.at;
     d->hot_bytes = ft.at.hot_words * 4;
     d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
     int optin = 0;
@@ -411,6 +426,10 @@ int init_device(const FlatTable& ft, DeviceState* d) {
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
     }
+    d->rt_bytes = (ft.at.classes[3] + (ft.at.total_words - ft.at.rt[0])) * 4;
+    d->rt_shared_ok = d->shared_ok && (int)d->rt_bytes + 1024 <= optin;
+    if (d->rt_shared_ok)
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
     CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
     for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
     CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
@@ -450,7 +469,9 @@ void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, c
 }
 void launch_roundtrip(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint8_t* status,
                       unsigned long long* dc) {
-    if (use_shared(d, n))
+    if (use_shared(d, n) && d->rt_shared_ok)
+        roundtrip_kernel<HotSharedRT><<<grid_shared(d, n), kBlockShared, d->rt_bytes, s>>>(d->view, words, n, status, dc);
+    else if (use_shared(d, n))
         roundtrip_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, status, dc);
     else
         roundtrip_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, status, dc);

@@ -45,7 +45,8 @@ struct FlatTable {
     std::vector<uint32_t> gfields;
     std::vector<uint32_t> gindex;    // per variant: first generator field | count << 24
     std::vector<uint32_t> metaf;     // MF_WORDS per variant
-    std::vector<uint32_t> rt;        // 8 per variant: roundtrip constants
+    std::vector<uint32_t> rt;        // 4 per variant: roundtrip constants {A0, A1, A2, E3 | mask index << 9}
+    std::vector<uint32_t> rt_masks;  // 4 per distinct mask: {~M0, ~M1, ~M2, reuse keep | const << 3}
     std::vector<VariantMeta> meta;
     uint32_t n_keys = 0;
     uint32_t n_buckets = 0;

@@ -37,7 +37,7 @@ void* mir_load(const char* path) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_file(path);
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), 0, m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), 0, 0, m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -46,7 +46,7 @@ void* mir_load_text(const char* text, uint64_t len) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_json_text(std::string(text, len));
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), m->flat.blob.data(), 0, m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), 0, 0, m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -75,7 +75,7 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
     for (uint64_t i = 0; i < n; ++i) {
         const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
         uint32_t start = 0, count = 0, steps = 0;
-        uint32_t ref = t.hot[t.at.dir + (c0 & 0xFFFu)];
+        uint32_t ref = t.cold[t.at.dir + (c0 & 0xFFFu)];
         if (ref) {
             while (!(ref & REF_LEAF)) {
                 ++steps;
@@ -85,12 +85,12 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
                     const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
                     child = ref_index(ref) + ((limb >> (bit & 31u)) & 1u);
                 } else {
-                    const uint32_t* na = t.hot + t.at.nodes[0] + ref_index(ref) * 4;
-                    const uint32_t* nb = t.hot + t.at.nodes[1] + ref_index(ref) * 4;
+                    const uint32_t* na = t.cold + t.at.nodes[0] + ref_index(ref) * 4;
+                    const uint32_t* nb = t.cold + t.at.nodes[1] + ref_index(ref) * 4;
                     const uint32_t f = (c0 & na[0]) ^ cb_rotl(c1 & na[1], nb[0]) ^ cb_rotl(c2 & na[2], nb[0] >> 5);
                     child = nb[1] + ((f * na[3]) >> nb[2]);
                 }
-                ref = t.hot[t.at.children + child];
+                ref = t.cold[t.at.children + child];
             }
             start = ref_index(ref); count = ref_count(ref);
         }
