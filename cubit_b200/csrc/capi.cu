@@ -42,36 +42,27 @@ constexpr int kBlockShared = 1024;   // table staged in shared memory, one CTA p
 constexpr uint64_t kSharedMinWords = 1u << 17;   // below this the staging copy is not worth it
 enum { CNT_DECODED = 0, CNT_REJECTED, CNT_TIE, CNT_EXACT, CNT_MISMATCH, CNT_WORDS };
 
-extern __shared__ uint4 g_table_smem[];
-
-// Gives the view the kernel works with: for HotShared the words [begin, end) of the blob are
-// first copied into dynamic shared memory by the whole CTA.
+// Copies the kernel's window of the blob into dynamic shared memory, by the whole CTA: words
+// [begin, end) for HotShared / HotSharedEnc, the roundtrip kernel's two ranges for HotSharedRT.
 template <class HOT>
-__device__ __forceinline__ FlatView stage_table(const FlatView& t, uint32_t, uint32_t) {
-    return t;
-}
-template <>
-__device__ __forceinline__ FlatView stage_table<HotShared>(const FlatView& t, uint32_t begin, uint32_t end) {
+__device__ __forceinline__ void stage_table(const FlatView&, uint32_t, uint32_t) {}
+__device__ __forceinline__ void stage_range(const FlatView& t, uint32_t begin, uint32_t end) {
     const uint4* src = reinterpret_cast<const uint4*>(t.cold + begin);
     const uint32_t quads = (end - begin) / 4;
-    for (uint32_t i = threadIdx.x; i < quads; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
+    for (uint32_t i = threadIdx.x; i < quads; i += blockDim.x) cb_table_smem[i] = __ldg(src + i);
     __syncthreads();
-    FlatView v = t;
-    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem) - begin * 4u;
-    return v;
 }
-// The roundtrip kernel's two ranges: blob words [0, rt_cut), then the roundtrip constants.
 template <>
-__device__ __forceinline__ FlatView stage_table<HotSharedRT>(const FlatView& t, uint32_t, uint32_t) {
+__device__ __forceinline__ void stage_table<HotShared>(const FlatView& t, uint32_t begin, uint32_t end) { stage_range(t, begin, end); }
+template <>
+__device__ __forceinline__ void stage_table<HotSharedEnc>(const FlatView& t, uint32_t begin, uint32_t end) { stage_range(t, begin, end); }
+template <>
+__device__ __forceinline__ void stage_table<HotSharedRT>(const FlatView& t, uint32_t, uint32_t) {
     const uint4* src = reinterpret_cast<const uint4*>(t.cold);
     const uint32_t quads_a = t.at.classes[3] / 4, first_b = t.at.rt[0] / 4, quads_b = (t.at.total_words - t.at.rt[0]) / 4;
-    for (uint32_t i = threadIdx.x; i < quads_a; i += blockDim.x) g_table_smem[i] = __ldg(src + i);
-    for (uint32_t i = threadIdx.x; i < quads_b; i += blockDim.x) g_table_smem[quads_a + i] = __ldg(src + first_b + i);
+    for (uint32_t i = threadIdx.x; i < quads_a; i += blockDim.x) cb_table_smem[i] = __ldg(src + i);
+    for (uint32_t i = threadIdx.x; i < quads_b; i += blockDim.x) cb_table_smem[quads_a + i] = __ldg(src + first_b + i);
     __syncthreads();
-    FlatView v = t;
-    v.hot_s = (uint32_t)__cvta_generic_to_shared(g_table_smem);
-    v.rt_s = v.hot_s + t.at.classes[3] * 4u - t.at.rt[0] * 4u;
-    return v;
 }
 
 // Adds per-thread tallies into the launch's counters: warp reduce, then one shared atomic
@@ -93,11 +84,12 @@ __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int
 }
 
 template <class HOT>
-__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
-    const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
+    stage_table<HOT>(tg, 0, tg.at.hot_words);
+    const FlatView& t = tg;
     uint32_t n_ok = 0, n_tie = 0;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -126,11 +118,12 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t
 // (even stride, aligned bases) a thread takes two neighbouring records with 64-bit loads, which
 // halves the number of load instructions; otherwise the two records are a grid stride apart.
 template <class HOT>
-__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __restrict__ slots,
               uint64_t slot_stride, const uint32_t* __restrict__ ctrl, uint64_t n, uint4* __restrict__ words, int paired) {
     // The encode kernel stages its own window: deposit and variant records.
-    const FlatView t = stage_table<HOT>(tg, tg.at.enc, tg.at.enc_end);
+    stage_table<HOT>(tg, tg.at.enc, tg.at.enc_end);
+    const FlatView& t = tg;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (paired) {
@@ -188,7 +181,8 @@ template <class HOT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
-    const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
+    stage_table<HOT>(tg, 0, tg.at.hot_words);
+    const FlatView& t = tg;
     uint32_t n_exact = 0, n_rejected = 0;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -210,11 +204,12 @@ roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8
 // (n_kernels + 1 entries) maps a word index to its kernel; results are combined per warp
 // when the whole warp sits in one kernel, else per lane.
 template <class HOT>
-__global__ void __launch_bounds__(std::is_same<HOT, HotShared>::value ? kBlockShared : kBlock)
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 meta_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, const uint64_t* __restrict__ word_start,
             uint32_t n_kernels, uint32_t* __restrict__ max_reg, uint32_t* __restrict__ barriers,
             uint8_t* __restrict__ exit_flag) {
-    const FlatView t = stage_table<HOT>(tg, 0, tg.at.hot_words);
+    stage_table<HOT>(tg, 0, tg.at.hot_words);
+    const FlatView& t = tg;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t base = (uint64_t)blockIdx.x * blockDim.x; base < n; base += step) {
         const uint64_t i = base + threadIdx.x;
@@ -414,7 +409,7 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     const uint32_t* blob = nullptr;
     const int rc = upload(c, d, ft.blob, &blob);
     if (rc) return rc;
-    d->view.cold = blob; d->view.hot_s = 0; d->view.rt_s = 0; d->view.at = ft.at;
+    d->view.cold = blob; d->view.at = ft.at;
     d->hot_bytes = ft.at.hot_words * 4;
     d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
     int optin = 0;
@@ -422,7 +417,7 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
     if (d->shared_ok) {
         CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotSharedEnc>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
     }
@@ -463,7 +458,7 @@ void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, c
     const int paired = (stride % 2 == 0) && ((uintptr_t)slots % 8 == 0) && ((uintptr_t)ctrl % 8 == 0) &&
                        ((uintptr_t)form % 4 == 0);
     if (use_shared(d, n))
-        encode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->enc_bytes, s>>>(d->view, form, slots, stride, ctrl, n, words, paired);
+        encode_kernel<HotSharedEnc><<<grid_shared(d, n), kBlockShared, d->enc_bytes, s>>>(d->view, form, slots, stride, ctrl, n, words, paired);
     else
         encode_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, form, slots, stride, ctrl, n, words, paired);
 }

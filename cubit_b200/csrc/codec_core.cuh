@@ -218,15 +218,8 @@ struct BlobLayout {
 
 struct FlatView {
     const uint32_t* cold;  // start of the blob (global memory on the device, host memory in the host build)
-    uint32_t hot_s;        // shared-memory address that blob offset 0 would have (HotShared only): the staged
-                           // window need not start at offset 0
-    uint32_t rt_s;         // the same for the roundtrip constants when they are staged (HotSharedRT)
     BlobLayout at;
 };
-// Kernels take the view by value and stage_table returns a changed copy; at 128 bytes the copy
-// stays in registers and constant-bank operands, above that the compiler lowers it differently
-// and the decode kernel loses a few percent.
-static_assert(sizeof(FlatView) <= 128, "FlatView grew past 128 bytes");
 
 enum : uint32_t { FORM_NONE = 0xFFFFu };
 enum : uint32_t { ST_OK = 0, ST_NO_OPCODE = 1, ST_NO_MATCH = 2 };
@@ -238,7 +231,9 @@ struct Quad { uint32_t x, y, z, w; };
 
 // How the hot part of the blob is read, by u32 offset from its start.  HotPlain works
 // everywhere (host, or plain device pointers); HotGlobal / HotShared are the two device
-// flavours.  HotShared addresses shared memory with 32-bit arithmetic only.
+// flavours.  HotShared addresses shared memory with 32-bit arithmetic only; the kernels read the
+// view straight from their parameters (it is never copied and changed), so its layout offsets
+// stay constant-bank operands.
 struct FlatView;
 // Besides w (one word) and q (one quad) of the hot part, a reader names two kinds of record
 // that a kernel may keep elsewhere: q3, the fourth quad of a class record (read only when rank
@@ -254,6 +249,9 @@ struct HotPlain {
     template <class V> static CB_HD Quad rt(const V& t, uint32_t off) { return q(t, off); }
 };
 #if defined(__CUDACC__)
+// The kernels' dynamic shared memory: the staged window of the blob starts at its first byte.
+extern __shared__ uint4 cb_table_smem[];
+__device__ __forceinline__ uint32_t cb_smem0() { return (uint32_t)__cvta_generic_to_shared(cb_table_smem); }
 struct HotGlobal {
     template <class V> static __device__ __forceinline__ uint32_t w(const V& t, uint32_t off) { return __ldg(t.cold + off); }
     template <class V> static __device__ __forceinline__ Quad q(const V& t, uint32_t off) {
@@ -267,14 +265,14 @@ struct HotGlobal {
 struct HotShared {
     template <class V> static __device__ __forceinline__ uint32_t w(const V& t, uint32_t off) {
         uint32_t v;
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(t.hot_s + off * 4u));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(cb_smem0() + off * 4u));
         return v;
     }
     template <class V> static __device__ __forceinline__ Quad q(const V& t, uint32_t off) {
         Quad r;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                     : "r"(t.hot_s + off * 4u));
+                     : "r"(cb_smem0() + off * 4u));
         return r;
     }
     template <class V> static __device__ __forceinline__ Quad q3(const V& t, uint32_t off) { return q(t, off); }
@@ -284,8 +282,13 @@ struct HotShared {
         return r;
     }
 };
+// The encode kernel's staging: blob words [enc, enc_end).
+struct HotSharedEnc {
+    template <class V> static __device__ __forceinline__ uint32_t w(const V& t, uint32_t off) { return HotShared::w(t, off - t.at.enc); }
+    template <class V> static __device__ __forceinline__ Quad q(const V& t, uint32_t off) { return HotShared::q(t, off - t.at.enc); }
+};
 // The roundtrip kernel's staging: blob words [0, rt_cut) and the roundtrip constants sit in
-// shared memory (the constants at rt_s), the fourth class quads and the extraction records
+// shared memory (the constants directly behind the first range), the fourth class quads and the extraction records
 // stay in global memory.
 struct HotSharedRT {
     template <class V> static __device__ __forceinline__ uint32_t w(const V& t, uint32_t off) { return HotShared::w(t, off); }
@@ -299,7 +302,7 @@ struct HotSharedRT {
         Quad r;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                     : "r"(t.rt_s + off * 4u));
+                     : "r"(cb_smem0() + (t.at.classes[3] - t.at.rt[0] + off) * 4u));
         return r;
     }
 };

@@ -37,7 +37,7 @@ void* mir_load(const char* path) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_file(path);
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), 0, 0, m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
@@ -46,7 +46,7 @@ void* mir_load_text(const char* text, uint64_t len) {
         Mirror* m = new Mirror;
         m->table = IsaTable::from_json_text(std::string(text, len));
         m->flat = FlatTable::compile(m->table);
-        m->view = FlatView{m->flat.blob.data(), 0, 0, m->flat.at};
+        m->view = FlatView{m->flat.blob.data(), m->flat.at};
         return m;
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
