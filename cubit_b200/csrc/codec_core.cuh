@@ -144,7 +144,7 @@ enum : uint32_t { KEY_WITHIN = 1u << 29 };
 enum : uint32_t { MEMO_MAX_CLASSES = 6, MEMO_BYTES = 16u << MEMO_MAX_CLASSES, MEMO_TIE = 0x80u, MEMO_WINNER_MASK = 0x1Fu };
 
 enum {                      // extraction record, 8 u32, hot; variants with the same field layout share one
-    XR_DESC = 0,            // [0..3] eight u16 slot descriptors: source shift | bits << 7 (bits 0..32)
+    XR_DESC = 0,            // [0..3] eight u16 slot descriptors: bits (0..32) | source shift << 6
     XR_MASK = 4,            // [4..6] layout 0: 1-bit field positions per limb; layout 1: all field bits per limb
     XR_CFG = 7,             // rot1 | rot2 << 5 | layout << 10 | synth_ok << 12
     XR_WORDS = 8,
@@ -392,6 +392,22 @@ CB_HD uint32_t cb_extract(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t src, u
     return __funnelshift_r(lo, hi, src) & cb_lowmask(nbits);   // the shift reads the low five bits of its amount
 #else
     return cb_funnel_r(lo, hi, src & 31u) & cb_lowmask(nbits);
+#endif
+}
+
+// Slot `half` (0 or 1) of a word of two 16-bit slot descriptors, each bits | source << 6: the
+// field is cut out of cc without first isolating the descriptor (the limb tests read the two
+// top bits of the source in place, the funnel shift ignores what lies above its five bits).
+CB_HD uint32_t cb_extract_desc(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t pair, uint32_t half) {
+    const uint32_t at = 16u * half;
+    const bool first = (pair & (0x60u << (6u + at))) == 0, second = (pair & (0x40u << (6u + at))) == 0;
+    const uint32_t lo = first ? c0 : (second ? c1 : c2);
+    const uint32_t hi = first ? c1 : (second ? c2 : 0u);
+    const uint32_t nbits = (pair >> at) & 63u;
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_r(lo, hi, pair >> (6u + at)) & cb_lowmask(nbits);
+#else
+    return cb_funnel_r(lo, hi, (pair >> (6u + at)) & 31u) & cb_lowmask(nbits);
 #endif
 }
 
@@ -649,8 +665,7 @@ CB_HD uint32_t extract_slots(const FlatView& t, uint32_t ext_index, uint32_t c0,
     } else {
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const uint32_t d = (desc[s >> 1] >> (16 * (s & 1))) & 0xFFFFu;
-            slots[s] = cb_extract(c0, c1, c2, d & 127u, d >> 7);
+            slots[s] = cb_extract_desc(c0, c1, c2, desc[s >> 1], s & 1);
         }
         slots[7] |= (c0 & m0) | cb_rotl(c1 & m1, cfg & 31u) | cb_rotl(c2 & m2, (cfg >> 5) & 31u);
     }

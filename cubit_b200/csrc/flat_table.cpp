@@ -719,7 +719,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
                     pos = next_slot * 32;
                     for (uint32_t part = 0, left = sb; left; ++part) {
                         const uint32_t take = std::min<uint32_t>(left, 32);
-                        const uint32_t d = (f.shift + 32 * part) | (take << 7);
+                        const uint32_t d = take | ((f.shift + 32 * part) << 6);
                         xr[XR_DESC + (next_slot >> 1)] |= d << (16 * (next_slot & 1));
                         ++next_slot;
                         left -= take;
@@ -894,7 +894,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             } else {
                 for (uint32_t s = 0; s < 8; ++s) {
                     const uint32_t d = (xr[XR_DESC + (s >> 1)] >> (16 * (s & 1))) & 0xFFFFu;
-                    const uint32_t src = d & 127u, take = d >> 7;
+                    const uint32_t take = d & 63u, src = d >> 6;
                     if (!take) continue;
                     const uint32_t w = src >> 5, sh = src & 31u;
                     const uint32_t ones = take >= 32 ? 0xFFFFFFFFu : ((1u << take) - 1u);
