@@ -64,9 +64,10 @@ CB_HD uint32_t ref_count(uint32_t r) { return (r >> 20) & 0xFFu; }
 enum {                      // hash node record, 8 u32 (two quads)
     NR_MASK = 0,            // [0..2] bits hashed at this node
     NR_MULT = 3,
-    NR_ROT = 4,             // rot1 | rot2 << 5 (a rotate reads the low five bits of its amount)
+    NR_ROT = 4,             // rotate amount for limb 1
     NR_CHILD = 5,           // first entry of the child table
     NR_SHIFT = 6,           // 32 - log2(child table size)
+    NR_ROT2 = 7,            // rotate amount for limb 2
     NR_WORDS = 8,
 };
 
@@ -425,7 +426,7 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
     while (!(ref & REF_LEAF)) {
         const uint32_t n = ref_index(ref) * 4u;
         const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
-        const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.x >> 5);
+        const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.w);
         ref = HOT::w(t, t.at.children + b.y + ((f * a.w) >> b.z));
     }
     *start = ref_index(ref);

@@ -424,7 +424,8 @@ struct TreeBuilder {
                 uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
                 for (int q = 0; q < 3; ++q) n[NR_MASK + q] = uint32_t(mask >> (32 * q));
                 n[NR_MULT] = m;
-                n[NR_ROT] = a | (b << 5);
+                n[NR_ROT] = a;
+                n[NR_ROT2] = b;
                 n[NR_CHILD] = child_base;
                 n[NR_SHIFT] = 32 - kk;
                 return REF_NODE | node;
@@ -499,7 +500,8 @@ struct TreeBuilder {
                 uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
                 for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
                 n[NR_MULT] = mult;
-                n[NR_ROT] = r1 | (r2 << 5);
+                n[NR_ROT] = r1;
+                n[NR_ROT2] = r2;
                 n[NR_CHILD] = child_base;
                 n[NR_SHIFT] = 32 - bits;
                 return REF_NODE | node;
