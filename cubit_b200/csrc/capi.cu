@@ -59,7 +59,7 @@ __device__ __forceinline__ void stage_table<HotSharedEnc>(const FlatView& t, uin
 template <>
 __device__ __forceinline__ void stage_table<HotSharedRT>(const FlatView& t, uint32_t, uint32_t) {
     const uint4* src = reinterpret_cast<const uint4*>(t.cold);
-    const uint32_t quads_a = t.at.classes[3] / 4, first_b = t.at.rt[0] / 4, quads_b = (t.at.total_words - t.at.rt[0]) / 4;
+    const uint32_t quads_a = t.at.sel_words / 4, first_b = t.at.rt[0] / 4, quads_b = (t.at.total_words - t.at.rt[0]) / 4;
     for (uint32_t i = threadIdx.x; i < quads_a; i += blockDim.x) cb_table_smem[i] = __ldg(src + i);
     for (uint32_t i = threadIdx.x; i < quads_b; i += blockDim.x) cb_table_smem[quads_a + i] = __ldg(src + first_b + i);
     __syncthreads();
@@ -421,7 +421,7 @@ int init_device(const FlatTable& ft, DeviceState* d) {
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
     }
-    d->rt_bytes = (ft.at.classes[3] + (ft.at.total_words - ft.at.rt[0])) * 4;
+    d->rt_bytes = (ft.at.sel_words + (ft.at.total_words - ft.at.rt[0])) * 4;
     d->rt_shared_ok = d->shared_ok && (int)d->rt_bytes + 1024 <= optin;
     if (d->rt_shared_ok)
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));

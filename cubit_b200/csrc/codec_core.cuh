@@ -144,13 +144,25 @@ enum : uint32_t { KEY_WITHIN = 1u << 29 };
 // number + 1 above its low MEMO_MAX_CLASSES bits.
 enum : uint32_t { MEMO_MAX_CLASSES = 6, MEMO_BYTES = 16u << MEMO_MAX_CLASSES, MEMO_TIE = 0x80u, MEMO_WINNER_MASK = 0x1Fu };
 
-enum {                      // extraction record, 8 u32, hot; variants with the same field layout share one
-    XR_DESC = 0,            // [0..3] eight u16 slot descriptors: bits (0..32) | source shift << 6
-    XR_MASK = 4,            // [4..6] layout 0: 1-bit field positions per limb; layout 1: all field bits per limb
-    XR_CFG = 7,             // rot1 | rot2 << 5 | layout << 10 | synth_ok << 24 (where ctrl keeps those bits)
-    XR_WORDS = 8,
+// Extraction record, 16 u32 (four quads), hot; variants with the same field layout share one.
+// Layout 0 gives every multi-bit field a slot of its own by the limb it lies in (no stored
+// field crosses a 32-bit limb there): slots 0..2 read limb 0, slot 3 limb 1, slot 4 limb 2,
+// slots 5 and 6 limb 1 or limb 2.  A field of `bits` bits at bit `sh` of its limb is cut out
+// as ((limb * 2^(32 - sh - bits)) mod 2^32) >> (32 - bits): the multiply drops everything above
+// the field and runs on the multiply-add pipe, the shift brings the value down; an unused slot
+// has multiplier 0.  Slots 5 and 6 add the products of both limbs, one multiplier being 0.
+enum {
+    XR_MULT = 0,            // [0..8] multipliers: slot 0, 1, 2 (limb 0), 3 (limb 1), 4 (limb 2), 5 (limb 1, limb 2), 6 (limb 1, limb 2)
+    XR_AMOUNT = 9,          // right-shift amounts (32 - bits) of slots 0..5, five bits each from bit 0
+    XR_CFG = 10,            // [4:0] amount of slot 6 | rot1 << 5 | rot2 << 10 | layout << 15 | synth_ok << 24 (where ctrl keeps those bits)
+    XR_MASK = 12,           // [12..14] layout 0: 1-bit field positions per limb; layout 1: all field bits per limb
+    XR_WORDS = 16,
 };
-enum { XC_LAYOUT_POS = 10, XC_SYNTH_POS = 24 };
+enum { XC_ROT1_POS = 5, XC_ROT2_POS = 10, XC_LAYOUT_POS = 15, XC_SYNTH_POS = 24 };
+enum { XR_N_MULT = 9 };
+// Slot and limb of each multiplier word.
+#define CB_XR_MULT_SLOT {0, 1, 2, 3, 4, 5, 5, 6, 6}
+#define CB_XR_MULT_LIMB {0, 0, 0, 1, 2, 1, 2, 1, 2}
 
 // Deposit record: the inverse of an extraction record, laid out for the encoder.  Slot s,
 // rotated left by its amount, lands every stored bit at its place in one or two limbs of the
@@ -199,10 +211,11 @@ struct BlobLayout {
     uint32_t dir;         // 4096 refs by opcode bits 11:0; 0 = no variant has these opcode bits
     // Records wider than 16 bytes are stored quad by quad (all first quads, then all second
     // quads, ...): a 16-byte stride spreads records over eight bank groups of shared memory.
-    uint32_t nodes[2], children, classes[4], broad[2], ext[2];   // in this order, except that the fourth class plane
-                          // follows the broad records: hot words [0, classes[3]) are all that variant selection reads
-                          // besides the fourth class quads
-    uint32_t hot_words;   // decode window: everything above lies below this offset
+    uint32_t nodes[2], children, classes[4], broad[2], ext[4];   // in this order, except that the fourth class plane
+                          // (read only when rank keys are compared) follows the extraction records and stays in
+                          // global memory
+    uint32_t sel_words;   // [0, sel_words) is all that variant selection reads besides the fourth class quads
+    uint32_t hot_words;   // decode window: selection tables and extraction records lie below this offset
     uint32_t enc;         // deposit records, six quad planes `enc_stride` words apart, one record per extraction record
     uint32_t enc_stride;
     uint32_t var[2];      // variant records (encode side, two quad planes) directly follow the deposit records
@@ -276,7 +289,7 @@ struct HotShared {
                      : "r"(cb_smem0() + off * 4u));
         return r;
     }
-    template <class V> static __device__ __forceinline__ Quad q3(const V& t, uint32_t off) { return q(t, off); }
+    template <class V> static __device__ __forceinline__ Quad q3(const V& t, uint32_t off) { return rt(t, off); }
     template <class V> static __device__ __forceinline__ Quad rt(const V& t, uint32_t off) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(t.cold + off));
         Quad r = {v.x, v.y, v.z, v.w};
@@ -288,7 +301,7 @@ struct HotSharedEnc {
     template <class V> static __device__ __forceinline__ uint32_t w(const V& t, uint32_t off) { return HotShared::w(t, off - t.at.enc); }
     template <class V> static __device__ __forceinline__ Quad q(const V& t, uint32_t off) { return HotShared::q(t, off - t.at.enc); }
 };
-// The roundtrip kernel's staging: blob words [0, rt_cut) and the roundtrip constants sit in
+// The roundtrip kernel's staging: blob words [0, sel_words) and the roundtrip constants sit in
 // shared memory (the constants directly behind the first range), the fourth class quads and the extraction records
 // stay in global memory.
 struct HotSharedRT {
@@ -303,7 +316,7 @@ struct HotSharedRT {
         Quad r;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                     : "r"(cb_smem0() + (t.at.classes[3] - t.at.rt[0] + off) * 4u));
+                     : "r"(cb_smem0() + (t.at.sel_words - t.at.rt[0] + off) * 4u));
         return r;
     }
 };
@@ -393,22 +406,6 @@ CB_HD uint32_t cb_extract(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t src, u
     return __funnelshift_r(lo, hi, src) & cb_lowmask(nbits);   // the shift reads the low five bits of its amount
 #else
     return cb_funnel_r(lo, hi, src & 31u) & cb_lowmask(nbits);
-#endif
-}
-
-// Slot `half` (0 or 1) of a word of two 16-bit slot descriptors, each bits | source << 6: the
-// field is cut out of cc without first isolating the descriptor (the limb tests read the two
-// top bits of the source in place, the funnel shift ignores what lies above its five bits).
-CB_HD uint32_t cb_extract_desc(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t pair, uint32_t half) {
-    const uint32_t at = 16u * half;
-    const bool first = (pair & (0x60u << (6u + at))) == 0, second = (pair & (0x40u << (6u + at))) == 0;
-    const uint32_t lo = first ? c0 : (second ? c1 : c2);
-    const uint32_t hi = first ? c1 : (second ? c2 : 0u);
-    const uint32_t nbits = (pair >> at) & 63u;
-#if defined(__CUDA_ARCH__)
-    return __funnelshift_r(lo, hi, pair >> (6u + at)) & cb_lowmask(nbits);
-#else
-    return cb_funnel_r(lo, hi, (pair >> (6u + at)) & 31u) & cb_lowmask(nbits);
 #endif
 }
 
@@ -652,25 +649,38 @@ CB_HD uint32_t ctrl_from_raw(uint32_t w0, uint32_t w3) {
     return ((w3 >> 9) & 0xFFFFFu) | ((w0 << 8) & 0xF00000u);
 }
 
+// High half of a 32 x 32 bit product.
+CB_HD uint32_t cb_mulhi(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    return __umulhi(a, b);
+#else
+    return (uint32_t)(((uint64_t)a * b) >> 32);
+#endif
+}
+
 // Field values of `variant` out of cc into the 8 slots; returns the variant's synth_ok bits at their
-// place in ctrl (bits 27:24).
+// place in ctrl (bits 27:24).  No branch: a layout 1 record has all multipliers zero and its limb
+// masks in XR_MASK, a layout 0 record has the 1-bit field positions there.
 template <class HOT>
 CB_HD uint32_t extract_slots(const FlatView& t, uint32_t ext_index, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t slots[8]) {
-    const Quad dq = HOT::q(t, t.at.ext[0] + ext_index * 4u), mq = HOT::q(t, t.at.ext[1] + ext_index * 4u);
-    const uint32_t desc[4] = {dq.x, dq.y, dq.z, dq.w};
-    const uint32_t cfg = mq.w;
-    const uint32_t m0 = mq.x, m1 = mq.y, m2 = mq.z;
-    if ((cfg >> XC_LAYOUT_POS) & 1u) {
-        slots[0] = c0 & m0; slots[1] = c1 & m1; slots[2] = c2 & m2;
-#pragma unroll
-        for (int s = 3; s < 8; ++s) slots[s] = 0;
-    } else {
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            slots[s] = cb_extract_desc(c0, c1, c2, desc[s >> 1], s & 1);
-        }
-        slots[7] |= (c0 & m0) | cb_rotl(c1 & m1, cfg & 31u) | cb_rotl(c2 & m2, (cfg >> 5) & 31u);
-    }
+    const uint32_t e = ext_index * 4u;
+    const Quad a = HOT::q(t, t.at.ext[0] + e), b = HOT::q(t, t.at.ext[1] + e);
+    const Quad c = HOT::q(t, t.at.ext[2] + e), d = HOT::q(t, t.at.ext[3] + e);
+    const uint32_t amount = c.y, cfg = c.z;
+    // The shifts read the low five bits of their amount.
+    const uint32_t y0 = cb_shr_wrap(c0 * a.x, amount);
+    const uint32_t y1 = cb_shr_wrap(c0 * a.y, amount >> 5);
+    const uint32_t y2 = cb_shr_wrap(c0 * a.z, amount >> 10);
+    slots[3] = cb_shr_wrap(c1 * a.w, amount >> 15);
+    slots[4] = cb_shr_wrap(c2 * b.x, amount >> 20);
+    slots[5] = cb_shr_wrap(c1 * b.y + c2 * b.z, amount >> 25);
+    slots[6] = cb_shr_wrap(c1 * b.w + c2 * c.x, cfg);
+    const uint32_t x0 = c0 & d.x, x1 = c1 & d.y, x2 = c2 & d.z;
+    const bool in_place = (cfg >> XC_LAYOUT_POS) & 1u;
+    slots[0] = in_place ? x0 : y0;
+    slots[1] = in_place ? x1 : y1;
+    slots[2] = in_place ? x2 : y2;
+    slots[7] = in_place ? 0u : (x0 | cb_rotl(x1, cfg >> XC_ROT1_POS) | cb_rotl(x2, cfg >> XC_ROT2_POS));
     return cfg & (0xFu << XC_SYNTH_POS);
 }
 

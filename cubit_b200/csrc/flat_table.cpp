@@ -670,17 +670,19 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         s.flags = fl;
 
         // ---- slot layout ---------------------------------------------------------------------
-        // Only field bits below bit 96 are stored.  Layout 0: multi-bit fields take slots from 0
-        // in table order (two slots above 32 stored bits), 1-bit fields share slot 7 at
+        // Only field bits below bit 96 are stored.  Layout 0: every multi-bit field has a slot of
+        // its own, chosen by the limb it lies in — limb 0 fields take slots 0, 1, 2; the first
+        // limb 1 field slot 3, further ones slots 5, 6; the first limb 2 field slot 4, further
+        // ones slots 6, 5 (each in table order) — and the 1-bit fields share slot 7 at
         // (source bit mod 32) rotated by a per-limb amount so that the three limbs do not
-        // collide.  Layout 1 (when that does not fit, or stored field ranges overlap): bits stay
-        // in place, slot k = limb k.
+        // collide.  Layout 1 (when a field crosses a limb boundary, the fields do not fit that
+        // pattern, or stored field ranges overlap): bits stay in place, slot k = limb k.
         auto stored_bits = [](const IsaField& f) -> uint32_t {
             return f.shift >= 96 ? 0u : std::min<uint32_t>(f.shift + f.bits, 96) - f.shift;
         };
         u128 stored_union = 0;
-        bool overlap = false;
-        uint32_t multi = 0;
+        bool overlap = false, crossing = false;
+        uint32_t per_limb[3] = {0, 0, 0};
         uint32_t fm[3] = {0, 0, 0};
         bool dup_flag = false;
         for (const IsaField& f : v.fields) {
@@ -692,8 +694,10 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             if (sb == 1) {
                 if (fm[f.shift >> 5] & (1u << (f.shift & 31))) dup_flag = true;
                 fm[f.shift >> 5] |= 1u << (f.shift & 31);
+            } else if ((f.shift >> 5) != ((f.shift + sb - 1) >> 5)) {
+                crossing = true;
             } else {
-                multi += sb > 32 ? 2 : 1;
+                ++per_limb[f.shift >> 5];
             }
         }
         const bool has_flags = (fm[0] | fm[1] | fm[2]) != 0;
@@ -704,10 +708,17 @@ FlatTable FlatTable::compile(const IsaTable& t) {
                 const uint32_t x = fm[0], y = cb_rotl(fm[1], a), z = cb_rotl(fm[2], b);
                 if (!(x & y) && !(x & z) && !(y & z)) { rot_ok = true; rot1 = a; rot2 = b; }
             }
-        const bool layout0 = !overlap && !dup_flag && rot_ok && multi + (has_flags ? 1 : 0) <= 8 && !(has_flags && multi > 7);
+        const uint32_t extra1 = per_limb[1] > 1 ? per_limb[1] - 1 : 0, extra2 = per_limb[2] > 1 ? per_limb[2] - 1 : 0;
+        const bool fits = per_limb[0] <= 3 && extra1 + extra2 <= 2;
+        const bool layout0 = !overlap && !dup_flag && !crossing && rot_ok && fits;
         m.layout_kind = layout0 ? 0 : 1;
         uint32_t* xr = &ft.ext[vi * XR_WORDS];
-        uint32_t next_slot = 0;
+        // Slots of the fields of limb 0, 1, 2 in the order they are handed out, and the multiplier
+        // word (XR_MULT + ...) that serves each (slot, limb) pair.
+        static const uint32_t kSlots[3][3] = {{0, 1, 2}, {3, 5, 6}, {4, 6, 5}};
+        static const uint32_t kMultWord[3][3] = {{0, 1, 2}, {3, 5, 7}, {4, 8, 6}};
+        uint32_t taken[3] = {0, 0, 0};
+        uint32_t amounts[7] = {0, 0, 0, 0, 0, 0, 0};
         const uint32_t gfield_start = uint32_t(ft.gfields.size());
         for (const IsaField& f : v.fields) {
             const uint32_t sb = stored_bits(f);
@@ -718,14 +729,11 @@ FlatTable FlatTable::compile(const IsaTable& t) {
                     const uint32_t limb = f.shift >> 5, bit = f.shift & 31, r = limb == 0 ? 0 : (limb == 1 ? rot1 : rot2);
                     pos = 7 * 32 + ((bit + r) & 31);
                 } else {
-                    pos = next_slot * 32;
-                    for (uint32_t part = 0, left = sb; left; ++part) {
-                        const uint32_t take = std::min<uint32_t>(left, 32);
-                        const uint32_t d = take | ((f.shift + 32 * part) << 6);
-                        xr[XR_DESC + (next_slot >> 1)] |= d << (16 * (next_slot & 1));
-                        ++next_slot;
-                        left -= take;
-                    }
+                    const uint32_t limb = f.shift >> 5, k = taken[limb]++;
+                    const uint32_t slot = kSlots[limb][k];
+                    pos = slot * 32;
+                    xr[XR_MULT + kMultWord[limb][k]] = 1u << (32u - (f.shift & 31u) - sb);
+                    amounts[slot] = 32u - sb;
                 }
             }
             FieldMeta fmeta;
@@ -735,6 +743,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             m.fields.push_back(fmeta);
             ft.gfields.push_back(f.shift | (f.bits << 7) | (gen_class(f) << 14) | ((sb ? pos : uint32_t(GF_NOT_STORED)) << 16));
         }
+        for (uint32_t s = 0; s < 6; ++s) xr[XR_AMOUNT] |= amounts[s] << (5 * s);
         const uint32_t gfield_count = uint32_t(ft.gfields.size()) - gfield_start;
         if (gfield_count > 255 || ft.gfields.size() >= (1u << 24)) throw std::runtime_error("too many fields in " + key);
         if (layout0) { xr[XR_MASK] = fm[0]; xr[XR_MASK + 1] = fm[1]; xr[XR_MASK + 2] = fm[2]; }
@@ -757,7 +766,8 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             }
         }
         m.synth_mask = synth;
-        xr[XR_CFG] = rot1 | (rot2 << 5) | (uint32_t(m.layout_kind) << XC_LAYOUT_POS) | (synth << XC_SYNTH_POS);
+        xr[XR_CFG] = amounts[6] | (rot1 << XC_ROT1_POS) | (rot2 << XC_ROT2_POS) | (uint32_t(m.layout_kind) << XC_LAYOUT_POS) |
+                     (synth << XC_SYNTH_POS);
         {
             std::vector<std::string> parts = split(key, '_');
             int skip = 0;
@@ -894,24 +904,22 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             if ((cfg >> XC_LAYOUT_POS) & 1u) {
                 for (uint32_t k = 0; k < 3; ++k) er[ER_MASK + 3 * k + k] = xr[XR_MASK + k];   // slot k is limb k, in place
             } else {
-                for (uint32_t s = 0; s < 8; ++s) {
-                    const uint32_t d = (xr[XR_DESC + (s >> 1)] >> (16 * (s & 1))) & 0xFFFFu;
-                    const uint32_t take = d & 63u, src = d >> 6;
-                    if (!take) continue;
-                    const uint32_t w = src >> 5, sh = src & 31u;
+                static const uint32_t kMultSlot[XR_N_MULT] = CB_XR_MULT_SLOT, kMultLimb[XR_N_MULT] = CB_XR_MULT_LIMB;
+                for (uint32_t w = 0; w < XR_N_MULT; ++w) {
+                    const uint32_t mult = xr[XR_MULT + w];
+                    if (!mult) continue;
+                    const uint32_t s = kMultSlot[w], limb = kMultLimb[w];
+                    const uint32_t right = ((s < 6 ? xr[XR_AMOUNT] >> (5 * s) : cfg) & 31u), take = 32u - right;
+                    const uint32_t sh = 32u - take - uint32_t(__builtin_ctz(mult));
                     const uint32_t ones = take >= 32 ? 0xFFFFFFFFu : ((1u << take) - 1u);
-                    const uint32_t lo = ones << sh, hi = sh ? ones >> (32u - sh) : 0u;
-                    if (w > 2 || (hi && w + 1 > 2)) throw std::runtime_error("stored field bits above bit 95");
-                    er[ER_MASK + 3 * s + w] |= lo;
-                    if (hi) er[ER_MASK + 3 * s + w + 1] |= hi;
+                    er[ER_MASK + 3 * s + limb] |= ones << sh;
                     amount[s] = sh;
-                    if (s == 7) amount7[0] = amount7[1] = amount7[2] = sh;
                 }
                 if (xr[XR_MASK] | xr[XR_MASK + 1] | xr[XR_MASK + 2]) {   // slot 7 holds the 1-bit fields of all limbs
                     for (uint32_t k = 0; k < 3; ++k) er[ER_MASK + 21 + k] = xr[XR_MASK + k];
                     amount7[0] = 0;
-                    amount7[1] = (32u - (cfg & 31u)) & 31u;
-                    amount7[2] = (32u - ((cfg >> 5) & 31u)) & 31u;
+                    amount7[1] = (32u - ((cfg >> XC_ROT1_POS) & 31u)) & 31u;
+                    amount7[2] = (32u - ((cfg >> XC_ROT2_POS) & 31u)) & 31u;
                 }
             }
             for (uint32_t s = 0; s < 6; ++s) rot_a[r] |= amount[s] << (5 * s);
@@ -968,10 +976,12 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     L.children = place(ft.children);
     for (size_t q = 0; q < 3; ++q) L.classes[q] = place(quad_plane(ft.classes, CR_WORDS, q));
     for (size_t q = 0; q < 2; ++q) L.broad[q] = place(quad_plane(ft.broad, BR_WORDS, q));
-    L.classes[3] = place(quad_plane(ft.classes, CR_WORDS, 3));   // the roundtrip kernel stages up to here
-    for (size_t q = 0; q < 2; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
+    while (ft.blob.size() % 4) ft.blob.push_back(0);
+    L.sel_words = uint32_t(ft.blob.size());   // the roundtrip kernel stages up to here
+    for (size_t q = 0; q < 4; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
+    L.classes[3] = place(quad_plane(ft.classes, CR_WORDS, 3));   // read only when rank keys are compared: not staged
     L.enc_stride = uint32_t(ft.enc.size() / ER_WORDS * 4);
     for (size_t q = 0; q < ER_WORDS / 4; ++q) {
         const uint32_t at = place(quad_plane(ft.enc, ER_WORDS, q));

@@ -692,12 +692,15 @@ KernelMetaResult infer_kernel_meta(const Oracle& o, const uint8_t* code, uint64_
 // ---------------------------------------------------------------------------------------
 
 // Only the part of a field below bit 96 is stored (the decoder never sees more).
-// Layout 0: multi-bit fields take slots from 0 in table order (two slots above 32 stored
-// bits); 1-bit fields share slot 7 at (source bit mod 32), rotated left by r1 for fields in
-// bits 63:32 and r2 for bits 95:64, (r1, r2) being the first pair in (0,0), (0,1), ... that
-// keeps the three groups apart.  Layout 1, when layout 0 does not fit (more than 8 slots,
-// flags with 8 multi-bit slots, two 1-bit fields on one bit, no rotation) or stored field
-// ranges overlap: every field stays at its position in the word.
+// Layout 0: every multi-bit field has a slot of its own, handed out by the 32-bit limb of the
+// word it lies in, in table order: fields of bits 31:0 take slots 0, 1, 2; of bits 63:32 slots
+// 3, 5, 6; of bits 95:64 slots 4, 6, 5.  1-bit fields share slot 7 at (source bit mod 32),
+// rotated left by r1 for fields in bits 63:32 and r2 for bits 95:64, (r1, r2) being the first
+// pair in (0,0), (0,1), ... that keeps the three groups apart.  Layout 1, when layout 0 does
+// not fit (a multi-bit field crosses a limb boundary, more than three fields in bits 31:0,
+// more than two fields beyond the first of bits 63:32 and the first of bits 95:64 together,
+// two 1-bit fields on one bit, no rotation) or stored field ranges overlap: every field stays
+// at its position in the word.
 const uint32_t NOT_STORED = 0xFFFFFFFFu;
 struct Layout {
     std::vector<uint32_t> pos, stored;
@@ -708,8 +711,8 @@ uint32_t rotl32(uint32_t x, uint32_t r) { return r ? ((x << r) | (x >> (32 - r))
 Layout slot_layout(const Entry& e) {
     Layout L;
     u128 used = 0;
-    bool overlap = false, dup = false;
-    uint32_t multi = 0, fm[3] = {0, 0, 0};
+    bool overlap = false, dup = false, crossing = false;
+    uint32_t in_limb[3] = {0, 0, 0}, fm[3] = {0, 0, 0};
     for (const Field& f : e.fields) {
         uint32_t sb = f.shift >= 96 ? 0 : std::min<uint32_t>(f.shift + f.bits, 96) - f.shift;
         L.stored.push_back(sb);
@@ -720,7 +723,8 @@ Layout slot_layout(const Entry& e) {
         if (sb == 1) {
             if (fm[f.shift >> 5] >> (f.shift & 31) & 1) dup = true;
             fm[f.shift >> 5] |= 1u << (f.shift & 31);
-        } else multi += sb > 32 ? 2 : 1;
+        } else if (f.shift / 32 != (f.shift + sb - 1) / 32) crossing = true;
+        else ++in_limb[f.shift / 32];
     }
     const bool flags = fm[0] | fm[1] | fm[2];
     uint32_t r1 = 0, r2 = 0;
@@ -730,8 +734,10 @@ Layout slot_layout(const Entry& e) {
             uint32_t x = fm[0], y = rotl32(fm[1], a), z = rotl32(fm[2], b);
             if (!(x & y) && !(x & z) && !(y & z)) { rot_ok = true; r1 = a; r2 = b; }
         }
-    L.kind = (!overlap && !dup && rot_ok && multi + (flags ? 1 : 0) <= 8) ? 0 : 1;
-    uint32_t slot = 0;
+    const uint32_t beyond = (in_limb[1] > 1 ? in_limb[1] - 1 : 0) + (in_limb[2] > 1 ? in_limb[2] - 1 : 0);
+    L.kind = (!overlap && !dup && !crossing && rot_ok && in_limb[0] <= 3 && beyond <= 2) ? 0 : 1;
+    const uint32_t order[3][3] = {{0, 1, 2}, {3, 5, 6}, {4, 6, 5}};
+    uint32_t next[3] = {0, 0, 0};
     for (size_t i = 0; i < e.fields.size(); ++i) {
         const Field& f = e.fields[i];
         const uint32_t sb = L.stored[i];
@@ -740,7 +746,7 @@ Layout slot_layout(const Entry& e) {
         else if (sb == 1) {
             const uint32_t limb = f.shift >> 5, r = limb == 0 ? 0 : (limb == 1 ? r1 : r2);
             L.pos.push_back(224 + (((f.shift & 31) + r) & 31));
-        } else { L.pos.push_back(slot * 32); slot += sb > 32 ? 2 : 1; }
+        } else L.pos.push_back(32 * order[f.shift / 32][next[f.shift / 32]++]);
     }
     return L;
 }
