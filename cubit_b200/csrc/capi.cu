@@ -83,18 +83,26 @@ __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int
         atomicAdd(&counters[threadIdx.x], (unsigned long long)s_acc[threadIdx.x]);
 }
 
-template <class HOT>
+// IDX is the type of the word index: uint32_t when the batch allows it (then every plane
+// address is one 32 x 32 + 64 bit multiply-add from a plane base that is the same for the
+// whole grid), uint64_t otherwise.  The next word of a thread is loaded before the current one
+// is decoded, so its latency hides behind the table walk.
+template <class HOT, class IDX>
 __global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
-decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t* __restrict__ form,
+decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n64, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
     stage_table<HOT>(tg, 0, tg.at.hot_words);
     const FlatView& t = tg;
     uint32_t n_ok = 0, n_tie = 0;
-    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
-    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    for (uint64_t i = first; i < n; i += step) {
-        const uint4 w = __ldcs(words + i);
+    const IDX n = (IDX)n64;
+    const IDX step = (IDX)gridDim.x * (IDX)blockDim.x;
+    const IDX first = (IDX)blockIdx.x * (IDX)blockDim.x + (IDX)threadIdx.x;
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (first < n) w = __ldcs(words + first);
+    for (IDX i = first; i < n; i += step) {
+        uint4 next = w;
+        if (n - i > step) next = __ldcs(words + (i + step));
         uint32_t f, c, s[8];
         decode_word<HOT>(t, w.x, w.y, w.z, w.w, &f, s, &c);
         __stcs(form + i, (uint16_t)f);
@@ -103,6 +111,7 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint16_t
         __stcs(ctrl + i, c);
         n_ok += (c >> 30) == ST_OK;
         n_tie += (c >> 28) & 1u;
+        w = next;
     }
     if (counters) {
         // Rejected words are the rest of this thread's share of the batch.
@@ -280,6 +289,7 @@ thread_local std::string g_create_error;
 struct DeviceState {
     int device = -1;
     int sm_count = 0;
+    bool wide_index = false;  // CUBIT_WIDE_INDEX=1: 64-bit word indices at every batch size (otherwise only above 2^31 words)
     bool shared_ok = false;   // the hot part of the table fits the opt-in shared memory of this device
     bool rt_shared_ok = false;   // so do the roundtrip kernel's two ranges (selection tables + roundtrip constants)
     uint32_t rt_bytes = 0;
@@ -411,12 +421,17 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     if (rc) return rc;
     d->view.cold = blob; d->view.at = ft.at;
     d->hot_bytes = ft.at.hot_words * 4;
+    {
+        const char* wide = getenv("CUBIT_WIDE_INDEX");
+        d->wide_index = wide && wide[0] == '1';
+    }
     d->enc_bytes = (ft.at.enc_end - ft.at.enc) * 4;
     int optin = 0;
     CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
     if (d->shared_ok) {
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotSharedEnc>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
         CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
@@ -447,10 +462,19 @@ int grid_shared(const DeviceState* d, uint64_t n) {
 
 void launch_decode(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint16_t* form, uint32_t* slots,
                    uint64_t stride, uint32_t* ctrl, unsigned long long* dc) {
-    if (use_shared(d, n))
-        decode_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
-    else
-        decode_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+    // 32-bit word indices while index + grid size cannot wrap.
+    const bool narrow = n < (1ull << 31) && !d->wide_index;
+    if (use_shared(d, n)) {
+        if (narrow)
+            decode_kernel<HotShared, uint32_t><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+        else
+            decode_kernel<HotShared, uint64_t><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+    } else {
+        if (narrow)
+            decode_kernel<HotGlobal, uint32_t><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+        else
+            decode_kernel<HotGlobal, uint64_t><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+    }
 }
 void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, const uint32_t* slots, uint64_t stride,
                    const uint32_t* ctrl, uint64_t n, uint4* words) {

@@ -29,8 +29,10 @@
 
 #if defined(__CUDACC__)
 #define CB_HD __host__ __device__ __forceinline__
+#define CB_HD_COLD __host__ __device__ __noinline__
 #else
 #define CB_HD inline
+#define CB_HD_COLD inline
 #endif
 
 namespace cubit {
@@ -40,7 +42,8 @@ namespace cubit {
 // Lookup structure: dir[word bits 11:0] -> ref.  A ref is a leaf (a run of
 // classes to test), a hash node or a bit node.  A hash node holds the mask bits that every
 // candidate below it checks; candidates that disagree on those bits cannot both match, so
-// the masked word is hashed (perfect hash, found on the host) into a child table of refs.
+// the masked word is hashed (one multiplier per limb, the products summed: a perfect hash found
+// on the host) into a child table of refs.
 // A bit node splits on one bit that most candidates below it check; candidates that do
 // not check it are listed under both children.  A class is a set of variants with
 // identical masks and constant bits: they match together and rank in a fixed order, so the
@@ -63,18 +66,18 @@ CB_HD uint32_t ref_count(uint32_t r) { return (r >> 20) & 0xFFu; }
 
 enum {                      // hash node record, 8 u32 (two quads)
     NR_MASK = 0,            // [0..2] bits hashed at this node
-    NR_MULT = 3,
-    NR_ROT = 4,             // rotate amount for limb 1
+    NR_MULT0 = 3,           // multiplier of limb 0
+    NR_MULT1 = 4,           // multiplier of limb 1
     NR_CHILD = 5,           // first entry of the child table
     NR_SHIFT = 6,           // 32 - log2(child table size)
-    NR_ROT2 = 7,            // rotate amount for limb 2
+    NR_MULT2 = 7,           // multiplier of limb 2
     NR_WORDS = 8,
 };
 
 enum {                      // class record, 16 u32 (four quads), hot; classes of a leaf are in static rank order
     CR_SMASK = 0,           // [0..2] strict match mask (guard bits 15:12 cleared)
     CR_SBASE = 3,           // [3..5] and_base & strict mask
-    CR_INFO = 6,            // broad record index | has_broad << 12 | members << 13 | tie_within << 21
+    CR_INFO = 6,            // broad record index | has_broad << 12 | several members << 13 | relevant broad records << 16
     CR_ANY_FLAGS = 7,       // [15:0] OR of the members' choice flags; [31:16] the same in every class of a leaf:
                             // which of the leaf's first 16 classes have a broad record
     CR_KEY = 8,             // static rank key of the best member
@@ -90,10 +93,9 @@ enum {                      // class record, 16 u32 (four quads), hot; classes o
 enum : uint32_t {           // CR_INFO
     CI_BROAD_MASK = 0xFFFu,
     CI_HAS_BROAD = 1u << 12,
-    CI_MEMBERS_POS = 13,          // 8 bits
-    CI_TIE_WITHIN = 1u << 21,     // best member shares its rank tuple with another member
-    CI_RELEVANT_POS = 22,         // 10 bits, the same in every class of a leaf: which of the leaf's first ten classes
-    CI_RELEVANT_BITS = 10,        // have a broad record that still matters when some class matched strictly
+    CI_SEVERAL = 1u << 13,        // the class has more than one member
+    CI_RELEVANT_POS = 16,         // 16 bits, the same in every class of a leaf: which of the leaf's first sixteen classes
+                                  // have a broad record that still matters when some class matched strictly
 };
 enum { BR_WORDS = 8 };      // broad record (hot): mask[3], base[3], pad
 // Per-flag table (cold) of a class with several members: for each of the 16 choice flags the
@@ -423,8 +425,8 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
     while (!(ref & REF_LEAF)) {
         const uint32_t n = ref_index(ref) * 4u;
         const Quad a = HOT::q(t, t.at.nodes[0] + n), b = HOT::q(t, t.at.nodes[1] + n);
-        const uint32_t f = (c0 & a.x) ^ cb_rotl(c1 & a.y, b.x) ^ cb_rotl(c2 & a.z, b.w);
-        ref = HOT::w(t, t.at.children + b.y + ((f * a.w) >> b.z));
+        const uint32_t f = (c0 & a.x) * a.w + (c1 & a.y) * b.x + (c2 & a.z) * b.w;
+        ref = HOT::w(t, t.at.children + b.y + (f >> b.z));
     }
     *start = ref_index(ref);
     *count = ref_count(ref);
@@ -502,7 +504,7 @@ CB_HD void fold_flagged(const FlatView& t, uint32_t ci, uint32_t prio, uint32_t 
     if (!(q1.w & need)) return;
     const Quad q2 = HOT::q(t, t.at.classes[2] + ci * 4u), q3 = HOT::q3(t, t.at.classes[3] + ci * 4u);
     uint32_t key = q2.x & ~KEY_WITHIN, best = q2.z, within = 0;
-    if (((q1.z >> CI_MEMBERS_POS) & 0xFFu) > 1u) {
+    if (q1.z & CI_SEVERAL) {
         const uint32_t f = cb_lowest_bit(need);
         const uint32_t* e = t.cold + t.at.flagbest + q3.w * FB_WORDS + 2u * f;
         key = cb_ld(e); best = cb_ld(e + 1);
@@ -518,17 +520,25 @@ CB_HD void fold_flagged(const FlatView& t, uint32_t ci, uint32_t prio, uint32_t 
     }
 }
 
-// Chooses the variant for cc.  Restates the candidate ranking and the ordered
-// disambiguation rules of reference src/decoder.rs:192-279 and :391-574 over static
-// per-variant flags: every rule asks for "the first candidate in rank order with flag F".
-// `best` returns variant | extraction record index << 16 of the winner.
+// Variant selection inside a leaf of more than 16 classes (none in the SM120 table; tables
+// that crowd many forms onto the same opcode bits have them): the same steps as
+// select_variant, 32 classes at a time, kept out of line.
+// (The few table offsets it needs travel by value: handing the whole view to an out-of-line
+// function would copy it to the stack.)
+struct WideLeafArgs {
+    const uint32_t* cold;
+    uint32_t classes[4], broad[2], flagbest, memo;
+};
 template <class HOT>
-CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c2,
-                              uint32_t* best, uint32_t* tie) {
+CB_HD_COLD uint32_t select_in_wide_leaf(WideLeafArgs wa, uint32_t start, uint32_t count, uint32_t c0, uint32_t c1, uint32_t c2,
+                                        uint32_t* best, uint32_t* tie) {
+    FlatView t;
+    t.cold = wa.cold;
+    for (int k = 0; k < 4; ++k) t.at.classes[k] = wa.classes[k];
+    t.at.broad[0] = wa.broad[0]; t.at.broad[1] = wa.broad[1];
+    t.at.flagbest = wa.flagbest; t.at.memo = wa.memo;
     *best = FORM_NONE;
     *tie = 0;
-    uint32_t start, count;
-    if (find_leaf<HOT>(t, c0, c1, c2, &start, &count) != ST_OK) return ST_NO_OPCODE;
 
     // Classes are tested 32 at a time into bit masks, collecting the union of choice flags over
     // the matching candidates.  Then the top-ranked candidate: the classes of a leaf are stored
@@ -546,7 +556,7 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         // branch would be taken by some lane of the warp in nearly every iteration).  Which
         // classes of the leaf have a broad record is a constant of the leaf, kept in the upper
         // half of every class's flag word for leaves of at most 16 classes.
-        uint32_t strict = 0, broad = 0, pending = 0, leaf_broad = 0, leaf_info = 0;
+        uint32_t strict = 0, broad = 0, pending = 0;
         {
             uint32_t bit = 1u;
 #pragma unroll 2
@@ -555,20 +565,10 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
                 const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
                 strict |= hit ? bit : 0u;
                 any |= hit ? b.w : 0u;
-                leaf_broad = b.w;
-                leaf_info = b.z;
             }
         }
-        if (count <= 16) {
-            // With a strict match, only the broad records the table compiler marked can still
-            // change the outcome (classes beyond the marked ten always count).
-            leaf_broad >>= 16;
-            const uint32_t relevant = (leaf_info >> CI_RELEVANT_POS) | ~((1u << CI_RELEVANT_BITS) - 1u);
-            pending = leaf_broad & ~strict & (strict ? relevant : 0xFFFFFFFFu);
-        } else {
-            for (uint32_t i = 0; i < chunk; ++i)
-                if (!((strict >> i) & 1u) && (HOT::w(t, t.at.classes[1] + (r0 + i) * 4u + 2u) & CI_HAS_BROAD)) pending |= 1u << i;
-        }
+        for (uint32_t i = 0; i < chunk; ++i)
+            if (!((strict >> i) & 1u) && (HOT::w(t, t.at.classes[1] + (r0 + i) * 4u + 2u) & CI_HAS_BROAD)) pending |= 1u << i;
         for (; pending; pending &= pending - 1u) {
             const uint32_t i = cb_lowest_bit(pending);
             const Quad b = HOT::q(t, t.at.classes[1] + (r0 + i) * 4u);
@@ -635,6 +635,125 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
                 const uint32_t prio = class_match<HOT>(t, start + i, c0, c1, c2, &fl);
                 if (prio != 3) fold_flagged<HOT>(t, start + i, prio, need, c0, c1, c2, &win_key, &win_best, &tie2);
             }
+        }
+        if (win_key != 0xFFFFFFFFu) { *best = win_best; *tie = tie_first | tie2; }
+    }
+    return ST_OK;
+}
+
+// Chooses the variant for cc.  Restates the candidate ranking and the ordered
+// disambiguation rules of reference src/decoder.rs:192-279 and :391-574 over static
+// per-variant flags: every rule asks for "the first candidate in rank order with flag F".
+// `best` returns variant | extraction record index << 16 of the winner.
+template <class HOT>
+CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c2,
+                              uint32_t* best, uint32_t* tie) {
+    *best = FORM_NONE;
+    *tie = 0;
+    uint32_t start, count;
+    if (find_leaf<HOT>(t, c0, c1, c2, &start, &count) != ST_OK) return ST_NO_OPCODE;
+    if (count > 16) {
+        WideLeafArgs wa;
+        wa.cold = t.cold;
+        for (int k = 0; k < 4; ++k) wa.classes[k] = t.at.classes[k];
+        wa.broad[0] = t.at.broad[0]; wa.broad[1] = t.at.broad[1];
+        wa.flagbest = t.at.flagbest; wa.memo = t.at.memo;
+        uint32_t wide_best, wide_tie;
+        const uint32_t st = select_in_wide_leaf<HOT>(wa, start, count, c0, c1, c2, &wide_best, &wide_tie);
+        *best = wide_best; *tie = wide_tie;
+        return st;
+    }
+
+    // Every leaf has at least one class (an empty one holds the class that never matches), so the
+    // first test runs for all lanes of a warp together.  Strict tests for every class first,
+    // collecting the union of choice flags over the matching candidates; the classes that failed
+    // but have a broad record are tested in a loop of their own (one word in three has one;
+    // inside the first loop the branch would be taken by some lane of the warp in nearly every
+    // iteration).  Which classes of the leaf have a broad record, and which of those still matter
+    // once some class matched strictly, are constants of the leaf kept in the upper halves of
+    // two words of every class.
+    const uint32_t at0 = t.at.classes[0] + start * 4u, at1 = t.at.classes[1] + start * 4u;
+    uint32_t strict, any, leaf_all, leaf_relevant;
+    {
+        const Quad a = HOT::q(t, at0), b = HOT::q(t, at1);
+        const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
+        strict = hit ? 1u : 0u;
+        any = hit ? b.w : 0u;
+        leaf_all = b.w;
+        leaf_relevant = b.z;
+    }
+    {
+        uint32_t bit = 2u;
+#pragma unroll 2
+        for (uint32_t i = 1; i < count; ++i, bit <<= 1) {
+            const Quad a = HOT::q(t, at0 + i * 4u), b = HOT::q(t, at1 + i * 4u);
+            const bool hit = (((c0 & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
+            strict |= hit ? bit : 0u;
+            any |= hit ? b.w : 0u;
+        }
+    }
+    uint32_t broad = 0;
+    for (uint32_t pending = ((strict ? leaf_relevant : leaf_all) >> 16) & ~strict; pending; pending &= pending - 1u) {
+        const uint32_t i = cb_lowest_bit(pending);
+        const Quad b = HOT::q(t, at1 + i * 4u);
+        const uint32_t br = (b.z & CI_BROAD_MASK) * 4u;
+        const Quad m = HOT::q(t, t.at.broad[0] + br), v = HOT::q(t, t.at.broad[1] + br);
+        const bool hit = (((c0 & m.x) ^ m.w) | ((c1 & m.y) ^ v.x) | ((c2 & m.z) ^ v.y)) == 0;
+        broad |= hit ? (1u << i) : 0u;
+        any |= hit ? b.w : 0u;
+    }
+    // The top-ranked candidate: the classes of a leaf are stored in static rank order, so the first
+    // strict match wins outright unless another match of its group (CR_GROUP) could overtake it
+    // through the word-dependent popcount; only then, or when broad matches are involved, are rank
+    // keys compared.  (No real key has both priority bits set, so the initial key never equals a tuple.)
+    uint32_t first_key = 0xFFFFFFFFu, first_fl = 0, first_best = FORM_NONE, tie_first = 0;
+    uint32_t mm = strict | broad;
+    const uint32_t at2 = t.at.classes[2] + start * 4u;
+    if (strict) {
+        // Strict matches outrank broad ones of the same score sign, and classes are stored by
+        // (score sign, ...): when the first strict match has a non-negative score no broad
+        // match can be on top, and the strict matches are ranked among themselves.
+        const uint32_t f = cb_lowest_bit(strict);
+        const Quad q2f = HOT::q(t, at2 + f * 4u);
+        if (broad == 0 || !(q2f.x >> 31)) {
+            const bool small = count <= MEMO_MAX_CLASSES;
+            const uint32_t memo = small ? (q2f.w >> MEMO_MAX_CLASSES) : 0u;
+            mm = q2f.w & strict;   // in a small leaf strict has no bit where the memo id sits
+            if (mm == (1u << f)) {
+                first_key = q2f.x; first_fl = q2f.y; first_best = q2f.z;
+                tie_first = (q2f.x & KEY_WITHIN) ? 1u : 0u;
+                mm = 0;
+            } else if (memo) {
+                const uint32_t at = (memo - 1u) * MEMO_BYTES + ((((c0 >> 12) & 15u) << MEMO_MAX_CLASSES) | strict);
+                const uint32_t e = (cb_ld(t.cold + t.at.memo + (at >> 2)) >> (8u * (at & 3u))) & 0xFFu;
+                const Quad q2 = HOT::q(t, at2 + (e & MEMO_WINNER_MASK) * 4u);
+                first_key = q2.x; first_fl = q2.y; first_best = q2.z;
+                tie_first = (e & MEMO_TIE) ? 1u : 0u;
+                mm = 0;
+            }
+        }
+    }
+    for (; mm; mm &= mm - 1u) {
+        const uint32_t i = cb_lowest_bit(mm);
+        const Quad q2 = HOT::q(t, at2 + i * 4u), q3 = HOT::q3(t, t.at.classes[3] + (start + i) * 4u);
+        const uint32_t k = (q2.x & ~KEY_WITHIN) | dynamic_key(q3, ((broad >> i) & 1u) << 1, c0, c1, c2);
+        const bool same = (k >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT), better = k < first_key;
+        tie_first = same ? 1u : (better ? ((q2.x & KEY_WITHIN) ? 1u : 0u) : tie_first);
+        first_fl = better ? q2.y : first_fl;
+        first_best = better ? q2.z : first_best;
+        first_key = better ? k : first_key;
+    }
+    if (first_key == 0xFFFFFFFFu) return ST_NO_MATCH;
+    *best = first_best;
+    *tie = tie_first;
+
+    const uint32_t need = choose_rule(any & 0xFFFFu, first_fl, c0, c1, c2);
+    if (need && !(first_fl & need)) {
+        // Second pass (uncommon): best member carrying `need` among the matching classes.
+        uint32_t win_key = 0xFFFFFFFFu, win_best = FORM_NONE, tie2 = 0;
+        for (uint32_t left = strict | broad; left; left &= left - 1u) {
+            const uint32_t i = cb_lowest_bit(left);
+            fold_flagged<HOT>(t, start + i, ((broad >> i) & 1u) << 1, need, c0, c1, c2, &win_key, &win_best, &tie2);
         }
         if (win_key != 0xFFFFFFFFu) { *best = win_best; *tie = tie_first | tie2; }
     }

@@ -244,7 +244,7 @@ struct TreeBuilder {
                 rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 1u : 0u);
                 rec[CR_BASE + k] = uint32_t(best.base96 >> (32 * k));
             }
-            uint32_t info = uint32_t(mem.size()) << CI_MEMBERS_POS;
+            uint32_t info = mem.size() > 1 ? uint32_t(CI_SEVERAL) : 0u;
             // The broad test only adds something when it can succeed where the strict one fails.
             if (best.b_ok && !(best.s_ok && best.bmask == best.smask)) {
                 auto found = broad_index.find({best.bmask, best.bbase});
@@ -258,11 +258,11 @@ struct TreeBuilder {
                 }
                 info |= found->second | CI_HAS_BROAD;
             }
-            if (mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT)) info |= CI_TIE_WITHIN;
+            const bool tie_within = mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT);
             rec[CR_INFO] = info;
             rec[CR_GROUP] = group_mask;
             rec[CR_FIRST_FLAGS] = best.flags;
-            rec[CR_KEY] = key_of[mem[0]] | ((info & CI_TIE_WITHIN) ? (uint32_t)KEY_WITHIN : 0u);
+            rec[CR_KEY] = key_of[mem[0]] | (tie_within ? (uint32_t)KEY_WITHIN : 0u);
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
             uint32_t any = 0;
             for (uint32_t v : mem) any |= st[v].flags & 0xFFFFu;
@@ -285,7 +285,7 @@ struct TreeBuilder {
             rec[CR_ANY_FLAGS] = any;
             if (ci < 16 && (info & CI_HAS_BROAD)) leaf_broad16 |= 1u << ci;
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
-            leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = (info & CI_TIE_WITHIN) ? 1u : 0u;
+            leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = tie_within ? 1u : 0u;
         }
         // Broad records that cannot change the outcome once some class matches strictly: every
         // strictly matchable class of the leaf has a non-negative score (so a strict match is on
@@ -302,7 +302,7 @@ struct TreeBuilder {
                 common &= rec[CR_FIRST_FLAGS];
                 if (rec[CR_KEY] >> 31) nonneg = false;
             }
-            for (size_t ci = 0; ci < order.size() && ci < CI_RELEVANT_BITS; ++ci) {
+            for (size_t ci = 0; ci < order.size() && ci < 16; ++ci) {
                 const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
                 if ((rec[CR_INFO] & CI_HAS_BROAD) && (!nonneg || (rec[CR_ANY_FLAGS] & 0xFFFFu & ~common))) leaf_relevant |= 1u << ci;
             }
@@ -355,8 +355,13 @@ struct TreeBuilder {
         return REF_LEAF | first_class | (uint32_t(order.size()) << 20);
     }
 
-    static uint32_t fold(u128 x, uint32_t r1, uint32_t r2) {
-        return uint32_t(x) ^ cb_rotl(uint32_t(x >> 32), r1) ^ cb_rotl(uint32_t(x >> 64), r2);
+    // The node hash before its final shift: one multiplier per limb, summed (three multiply-adds
+    // on the device).
+    static uint32_t mix(u128 x, const uint32_t m[3]) {
+        return uint32_t(x) * m[0] + uint32_t(x >> 32) * m[1] + uint32_t(x >> 64) * m[2];
+    }
+    static void draw_multipliers(uint64_t* rng, uint32_t m[3]) {
+        for (int k = 0; k < 3; ++k) { *rng = splitmix64(*rng); m[k] = uint32_t(*rng >> 16) | 1u; }
     }
 
     // A subtree of bit nodes becomes one hash node over its bits (at most kFlattenBits of them;
@@ -403,13 +408,12 @@ struct TreeBuilder {
         for (uint32_t extra = 0; extra < 4; ++extra) {
             const uint32_t kk = k + extra;
             for (uint32_t attempt = 0; attempt < 4000; ++attempt) {
-                rng = splitmix64(rng);
-                const uint32_t m = uint32_t(rng) | 1u;
-                const uint32_t a = (attempt / 64) % 32, b = (attempt / 7) % 32;
+                uint32_t m[3];
+                draw_multipliers(&rng, m);
                 std::vector<char> seen(size_t(1) << kk, 0);
                 bool clash = false;
                 for (const u128& x : pattern) {
-                    const uint32_t h = kk ? (fold(x, a, b) * m) >> (32 - kk) : 0u;
+                    const uint32_t h = kk ? mix(x, m) >> (32 - kk) : 0u;
                     if (seen[h]) { clash = true; break; }
                     seen[h] = 1;
                 }
@@ -420,12 +424,12 @@ struct TreeBuilder {
                 if (child_base + (size_t(1) << kk) >= (1u << 20)) throw std::runtime_error("match tree too large");
                 ft.children.resize(ft.children.size() + (size_t(1) << kk), REF_LEAF);
                 for (size_t i = 0; i < pattern.size(); ++i)
-                    ft.children[child_base + ((fold(pattern[i], a, b) * m) >> (32 - kk))] = target[i];
+                    ft.children[child_base + (kk ? mix(pattern[i], m) >> (32 - kk) : 0u)] = target[i];
                 uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
                 for (int q = 0; q < 3; ++q) n[NR_MASK + q] = uint32_t(mask >> (32 * q));
-                n[NR_MULT] = m;
-                n[NR_ROT] = a;
-                n[NR_ROT2] = b;
+                n[NR_MULT0] = m[0];
+                n[NR_MULT1] = m[1];
+                n[NR_MULT2] = m[2];
                 n[NR_CHILD] = child_base;
                 n[NR_SHIFT] = 32 - kk;
                 return REF_NODE | node;
@@ -468,23 +472,22 @@ struct TreeBuilder {
             // Perfect hash of the masked word into a power-of-two child table.
             uint32_t bits = 1;
             while ((1u << bits) < parts.size()) ++bits;
-            uint32_t mult = 0, r1 = 0, r2 = 0;
+            uint32_t mult[3] = {0, 0, 0};
             bool ok = false;
             uint64_t rng = 0x243F6A8885A308D3ull ^ (uint64_t(vs[0]) << 20) ^ depth;
             for (uint32_t extra = 0; extra < 3 && !ok; ++extra) {
                 const uint32_t k = bits + extra;
                 for (uint32_t attempt = 0; attempt < 4000 && !ok; ++attempt) {
-                    rng = splitmix64(rng);
-                    const uint32_t m = uint32_t(rng) | 1u;
-                    const uint32_t a = (attempt / 64) % 32, b = (attempt / 7) % 32;
+                    uint32_t m[3];
+                    draw_multipliers(&rng, m);
                     std::vector<char> seen(size_t(1) << k, 0);
                     bool clash = false;
                     for (const auto& kv : parts) {
-                        const uint32_t h = (fold(kv.first, a, b) * m) >> (32 - k);
+                        const uint32_t h = mix(kv.first, m) >> (32 - k);
                         if (seen[h]) { clash = true; break; }
                         seen[h] = 1;
                     }
-                    if (!clash) { ok = true; mult = m; r1 = a; r2 = b; bits = k; }
+                    if (!clash) { ok = true; mult[0] = m[0]; mult[1] = m[1]; mult[2] = m[2]; bits = k; }
                 }
             }
             if (ok) {
@@ -493,15 +496,15 @@ struct TreeBuilder {
                 const uint32_t child_base = uint32_t(ft.children.size());
                 ft.children.resize(ft.children.size() + (size_t(1) << bits), REF_LEAF);   // empty leaf: nothing matches
                 for (const auto& kv : parts) {
-                    const uint32_t h = (fold(kv.first, r1, r2) * mult) >> (32 - bits);
+                    const uint32_t h = mix(kv.first, mult) >> (32 - bits);
                     const uint32_t ref = build(kv.second, used | common, depth + 1);
                     ft.children[child_base + h] = ref;
                 }
                 uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
                 for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
-                n[NR_MULT] = mult;
-                n[NR_ROT] = r1;
-                n[NR_ROT2] = r2;
+                n[NR_MULT0] = mult[0];
+                n[NR_MULT1] = mult[1];
+                n[NR_MULT2] = mult[2];
                 n[NR_CHILD] = child_base;
                 n[NR_SHIFT] = 32 - bits;
                 return REF_NODE | node;
@@ -955,6 +958,19 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     }
     tb.flatten_all(dir);
     ft.max_depth = tb.max_depth;
+    // An empty leaf (opcode bits that only unmatchable variants have, an unused entry of a hash
+    // node's child table) becomes a leaf of one class that never matches, so that every leaf the
+    // kernels reach has a first class to test.
+    {
+        const uint32_t never = uint32_t(ft.classes.size() / CR_WORDS);
+        if (never >= (1u << 20)) throw std::runtime_error("match tree too large");
+        uint32_t rec[CR_WORDS] = {0};
+        rec[CR_SBASE] = 1;   // (cc & 0) ^ 1 is never 0
+        ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
+        const uint32_t empty = REF_LEAF, filled = REF_LEAF | never | (1u << 20);
+        for (uint32_t& r : dir) if (r == empty) r = filled;
+        for (uint32_t& r : ft.children) if (r == empty) r = filled;
+    }
     if (ft.broad.empty()) ft.broad.assign(BR_WORDS, 0);
 
     // One blob: hot sections first, each 16-byte aligned.

@@ -87,8 +87,8 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
                 } else {
                     const uint32_t* na = t.cold + t.at.nodes[0] + ref_index(ref) * 4;
                     const uint32_t* nb = t.cold + t.at.nodes[1] + ref_index(ref) * 4;
-                    const uint32_t f = (c0 & na[0]) ^ cb_rotl(c1 & na[1], nb[0]) ^ cb_rotl(c2 & na[2], nb[3]);
-                    child = nb[1] + ((f * na[3]) >> nb[2]);
+                    const uint32_t f = (c0 & na[0]) * na[3] + (c1 & na[1]) * nb[0] + (c2 & na[2]) * nb[3];
+                    child = nb[1] + (f >> nb[2]);
                 }
                 ref = t.cold[t.at.children + child];
             }
