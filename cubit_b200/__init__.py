@@ -48,9 +48,19 @@ def decode_kernel(cubin_path, kernel_name: str) -> list:
     return default_codec().decode_kernel(cubin_path, kernel_name)
 
 
+_host_only: Codec | None = None
+
+
 def table_info() -> tuple:
-    """(number of instruction keys, number of encoding variants)."""
-    return default_codec().table_info()
+    """(number of instruction keys, number of encoding variants).  Answered from the table alone, so it
+    also works on a machine without a GPU."""
+    global _host_only
+    with _lock:
+        if _default is not None:
+            return _default.table_info()
+        if _host_only is None:
+            _host_only = Codec(devices=())
+        return _host_only.table_info()
 
 
 def encode(sass: str, addr: int = 0) -> tuple:

@@ -163,7 +163,8 @@ class Codec:
         """decode_batch for at most STATIC_MAX_WORDS words without any device allocation: the batch is
         staged through a fixed array built into the library.  For callers that must not call cudaMalloc
         while running (device memory reserved by someone else, or no tolerance for its implicit
-        synchronisation).  Calls on one device must not overlap."""
+        synchronisation).  All calls on one GPU share that array, from whichever Codec; the library
+        serialises them with one lock per GPU, so they are safe but do not run in parallel."""
         w = self._words(words)
         n = len(w)
         form = np.empty(n, np.uint16); slots = np.empty((8, n), np.uint32); ctrl = np.empty(n, np.uint32)

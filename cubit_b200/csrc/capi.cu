@@ -281,6 +281,11 @@ constexpr uint64_t kStaticCtrlOff = kStaticSlotsOff + kStaticMaxWords * 32;
 constexpr uint64_t kStaticCountersOff = kStaticCtrlOff + kStaticMaxWords * 4;
 constexpr uint64_t kStaticBytes = kStaticCountersOff + 256;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+// One array per GPU whatever the number of contexts: its users are serialised per device ordinal,
+// and its device address there is looked up once.
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mu[kMaxStaticDevices];
+unsigned char* g_static_addr[kMaxStaticDevices] = {nullptr};
 
 // ---- context -----------------------------------------------------------------------------
 
@@ -306,8 +311,6 @@ struct DeviceState {
     cudaStream_t stream = nullptr, stream2 = nullptr;
     cudaEvent_t event = nullptr;
     std::mutex stage_mu;
-    // Device address of g_static_scratch on this device, looked up on first use.
-    unsigned char* static_scratch = nullptr;
     // Stream generator tables, one per (mix, seed).
     std::map<std::pair<uint32_t, uint64_t>, SynthView> synth;
 };
@@ -372,6 +375,19 @@ int translate_exception(const cubit_ctx* ctx) noexcept {
         cudaError_t e_ = (call);                                                                      \
         if (e_ != cudaSuccess)                                                                        \
             return fail(ctx, CUBIT_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));     \
+    } while (0)
+
+// The same for calls that follow asynchronous work on `stream`: what was queued is waited for
+// before the error is returned, so that nothing still writes into the caller's buffers, local
+// arrays or the staging area when the staging lock is dropped.
+#define CU_TRY_DRAIN(ctx, stream, call)                                                               \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess) {                                                                      \
+            cudaStreamSynchronize(stream);                                                            \
+            cudaGetLastError();                                                                       \
+            return fail(ctx, CUBIT_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));     \
+        }                                                                                             \
     } while (0)
 
 // Frees what one device of a context holds; the device is made current first.
@@ -538,9 +554,14 @@ int run_counted(cubit_ctx* ctx, DeviceState* d, cudaStream_t stream, cubit_count
     cudaError_t e = cudaMemsetAsync(dc, 0, sizeof host, stream);
     if (e == cudaSuccess) { launch(dc); e = cudaGetLastError(); }
     if (e == cudaSuccess) e = cudaMemcpyAsync(host, dc, sizeof host, cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    // The slot goes back only when nothing queued above can still write to it or to `host`.
+    const cudaError_t waited = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = waited;
     give_counter_slot(d, slot);
-    if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string("counted launch: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, CUBIT_ERR_CUDA, std::string("counted launch: ") + cudaGetErrorString(e));
+    }
     add_counts(counts, host);
     return CUBIT_OK;
 }
@@ -563,17 +584,25 @@ constexpr uint64_t kChunkWords = 1ull << 22;   // host paths stream the batch in
 
 uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-// Host-memory decode of words [begin, end) on one device.  The range is cut into chunks that
-// alternate between two halves of the staging area and two streams, so the copy-in of one
+// One chunk of a host batch on its way through the device: the stream it is queued on, its half
+// of the staging area, the first item and the number of items, and the counter slot of the call.
+struct ChunkIO {
+    cudaStream_t stream;
+    uint8_t* stage;
+    uint64_t at, items;
+    unsigned long long* counters;
+};
+
+// Streams items [begin, end) of a host batch through one device.  The range is cut into chunks
+// that alternate between two halves of the staging area and two streams, so the copy-in of one
 // chunk, the kernel of another and the copy-out of a third overlap (the PCIe link is full
-// duplex); with pinned host buffers every copy is asynchronous.
-int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t n_total, uint64_t begin,
-                      uint64_t end, uint16_t* form, uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
-    std::lock_guard<std::mutex> g(d->stage_mu);
-    CU_TRY(ctx, cudaSetDevice(d->device));
-    const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
-    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
-    const uint64_t o_ctrl = o_slots + chunk * 32, half = align_up(o_ctrl + chunk * 4, 256);
+// duplex); with pinned host buffers every copy is asynchronous.  `body` queues the copies and
+// the launch of one chunk on the chunk's stream and returns the first CUDA error it met.
+// The caller holds the device's staging lock and has made the device current.  Whatever fails,
+// nothing is left running on either stream when this returns.
+template <typename Body>
+int pipeline_host_range(cubit_ctx* ctx, DeviceState* d, uint64_t begin, uint64_t end, uint64_t chunk, uint64_t half,
+                        cubit_counts* counts, const char* what, Body body) {
     const bool two = end - begin > chunk;
     int rc = ensure_stage(ctx, d, two ? 2 * half : half);
     if (rc) return rc;
@@ -592,60 +621,83 @@ int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint
         if (e == cudaSuccess) e = cudaStreamWaitEvent(streams[1], d->event, 0);
     }
     uint64_t k = 0;
-    for (uint64_t at = begin; at < end && e == cudaSuccess; at += chunk, ++k) {
-        const uint64_t m = std::min(chunk, end - at);
-        cudaStream_t s = streams[k & 1];
-        uint8_t* st = (uint8_t*)d->stage + (k & 1) * half;
-        e = cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, s);
-        if (e != cudaSuccess) break;
-        launch_decode(d, s, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), chunk,
-                      (uint32_t*)(st + o_ctrl), dc);
-        e = cudaGetLastError();
-        if (e == cudaSuccess) e = cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, s);
-        for (int p = 0; p < 8 && e == cudaSuccess; ++p)
-            e = cudaMemcpyAsync(slots + (uint64_t)p * n_total + at, st + o_slots + (uint64_t)p * chunk * 4, m * 4,
-                                cudaMemcpyDeviceToHost, s);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, s);
-    }
+    for (uint64_t at = begin; at < end && e == cudaSuccess; at += chunk, ++k)
+        e = body(ChunkIO{streams[k & 1], (uint8_t*)d->stage + (k & 1) * half, at, std::min(chunk, end - at), dc});
     unsigned long long host[CNT_WORDS] = {0, 0, 0, 0, 0};
     if (e == cudaSuccess) e = cudaStreamSynchronize(streams[1]);
     if (e == cudaSuccess && dc) e = cudaMemcpyAsync(host, dc, sizeof host, cudaMemcpyDeviceToHost, streams[0]);
     if (e == cudaSuccess) e = cudaStreamSynchronize(streams[0]);
-    if (e != cudaSuccess) {   // nothing may still be using the staging area or the counter slot
+    if (e != cudaSuccess) {   // nothing may still be using the staging area, the caller's buffers or the counter slot
         cudaStreamSynchronize(streams[0]);
         cudaStreamSynchronize(streams[1]);
         cudaGetLastError();
     }
     if (slot >= 0) give_counter_slot(d, slot);
-    if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string("host decode: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(ctx, CUBIT_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
     if (counts) add_counts(counts, host);
     return CUBIT_OK;
+}
+
+// Staging layout of one chunk of records: words, then the form, slot and ctrl planes.
+struct RecordStage {
+    uint64_t chunk, o_form, o_slots, o_ctrl, half;
+    explicit RecordStage(uint64_t items) {
+        chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(items, 1));
+        o_form = align_up(chunk * 16, 256);
+        o_slots = o_form + align_up(chunk * 2, 256);
+        o_ctrl = o_slots + chunk * 32;
+        half = align_up(o_ctrl + chunk * 4, 256);
+    }
+};
+
+// Queues the copy of one chunk's records from the staging area to host planes that are
+// `host_stride` records apart, record `at` of the call landing at `host_at`.
+cudaError_t records_to_host(const RecordStage& L, const ChunkIO& io, uint64_t host_at, uint64_t host_stride, uint16_t* form,
+                            uint32_t* slots, uint32_t* ctrl) {
+    cudaError_t e = cudaSuccess;
+    if (form) e = cudaMemcpyAsync(form + host_at, io.stage + L.o_form, io.items * 2, cudaMemcpyDeviceToHost, io.stream);
+    for (int p = 0; p < 8 && e == cudaSuccess && slots; ++p)
+        e = cudaMemcpyAsync(slots + (uint64_t)p * host_stride + host_at, io.stage + L.o_slots + (uint64_t)p * L.chunk * 4,
+                            io.items * 4, cudaMemcpyDeviceToHost, io.stream);
+    if (e == cudaSuccess && ctrl) e = cudaMemcpyAsync(ctrl + host_at, io.stage + L.o_ctrl, io.items * 4, cudaMemcpyDeviceToHost, io.stream);
+    return e;
+}
+
+// Host-memory decode of words [begin, end) on one device.
+int decode_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t n_total, uint64_t begin,
+                      uint64_t end, uint16_t* form, uint32_t* slots, uint32_t* ctrl, cubit_counts* counts) {
+    std::lock_guard<std::mutex> g(d->stage_mu);
+    CU_TRY(ctx, cudaSetDevice(d->device));
+    const RecordStage L(end - begin);
+    return pipeline_host_range(ctx, d, begin, end, L.chunk, L.half, counts, "host decode", [&](const ChunkIO& io) {
+        cudaError_t e = cudaMemcpyAsync(io.stage, words + io.at * 16, io.items * 16, cudaMemcpyHostToDevice, io.stream);
+        if (e != cudaSuccess) return e;
+        launch_decode(d, io.stream, (const uint4*)io.stage, io.items, (uint16_t*)(io.stage + L.o_form),
+                      (uint32_t*)(io.stage + L.o_slots), L.chunk, (uint32_t*)(io.stage + L.o_ctrl), io.counters);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = records_to_host(L, io, io.at, n_total, form, slots, ctrl);
+        return e;
+    });
 }
 
 int encode_host_range(cubit_ctx* ctx, DeviceState* d, const uint16_t* form, const uint32_t* slots, const uint32_t* ctrl,
                       uint64_t n_total, uint64_t begin, uint64_t end, uint8_t* words) {
     std::lock_guard<std::mutex> g(d->stage_mu);
     CU_TRY(ctx, cudaSetDevice(d->device));
-    const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
-    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
-    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
-    int rc = ensure_stage(ctx, d, total);
-    if (rc) return rc;
-    uint8_t* st = (uint8_t*)d->stage;
-    for (uint64_t at = begin; at < end; at += chunk) {
-        const uint64_t m = std::min(chunk, end - at);
-        CU_TRY(ctx, cudaMemcpyAsync(st + o_form, form + at, m * 2, cudaMemcpyHostToDevice, d->stream));
-        for (int k = 0; k < 8; ++k)
-            CU_TRY(ctx, cudaMemcpyAsync(st + o_slots + (uint64_t)k * chunk * 4, slots + (uint64_t)k * n_total + at, m * 4,
-                                        cudaMemcpyHostToDevice, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(st + o_ctrl, ctrl + at, m * 4, cudaMemcpyHostToDevice, d->stream));
-        launch_encode(d, d->stream, (const uint16_t*)(st + o_form), (const uint32_t*)(st + o_slots), chunk,
-                      (const uint32_t*)(st + o_ctrl), m, (uint4*)st);
-        CU_TRY(ctx, cudaGetLastError());
-        CU_TRY(ctx, cudaMemcpyAsync(words + at * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
-    }
-    return CUBIT_OK;
+    const RecordStage L(end - begin);
+    return pipeline_host_range(ctx, d, begin, end, L.chunk, L.half, nullptr, "host encode", [&](const ChunkIO& io) {
+        cudaError_t e = cudaMemcpyAsync(io.stage + L.o_form, form + io.at, io.items * 2, cudaMemcpyHostToDevice, io.stream);
+        for (int k = 0; k < 8 && e == cudaSuccess; ++k)
+            e = cudaMemcpyAsync(io.stage + L.o_slots + (uint64_t)k * L.chunk * 4, slots + (uint64_t)k * n_total + io.at,
+                                io.items * 4, cudaMemcpyHostToDevice, io.stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(io.stage + L.o_ctrl, ctrl + io.at, io.items * 4, cudaMemcpyHostToDevice, io.stream);
+        if (e != cudaSuccess) return e;
+        launch_encode(d, io.stream, (const uint16_t*)(io.stage + L.o_form), (const uint32_t*)(io.stage + L.o_slots), L.chunk,
+                      (const uint32_t*)(io.stage + L.o_ctrl), io.items, (uint4*)io.stage);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(words + io.at * 16, io.stage, io.items * 16, cudaMemcpyDeviceToHost, io.stream);
+        return e;
+    });
 }
 
 int roundtrip_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, uint64_t begin, uint64_t end,
@@ -653,21 +705,15 @@ int roundtrip_host_range(cubit_ctx* ctx, DeviceState* d, const uint8_t* words, u
     std::lock_guard<std::mutex> g(d->stage_mu);
     CU_TRY(ctx, cudaSetDevice(d->device));
     const uint64_t chunk = std::min<uint64_t>(kChunkWords, std::max<uint64_t>(end - begin, 1));
-    const uint64_t o_status = align_up(chunk * 16, 256), total = o_status + chunk;
-    int rc = ensure_stage(ctx, d, total);
-    if (rc) return rc;
-    uint8_t* st = (uint8_t*)d->stage;
-    for (uint64_t at = begin; at < end; at += chunk) {
-        const uint64_t m = std::min(chunk, end - at);
-        CU_TRY(ctx, cudaMemcpyAsync(st, words + at * 16, m * 16, cudaMemcpyHostToDevice, d->stream));
-        rc = run_counted(ctx, d, d->stream, counts, [&](unsigned long long* dc) {
-            launch_roundtrip(d, d->stream, (const uint4*)st, m, st + o_status, dc);
-        });
-        if (rc) return rc;
-        CU_TRY(ctx, cudaMemcpyAsync(status + at, st + o_status, m, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
-    }
-    return CUBIT_OK;
+    const uint64_t o_status = align_up(chunk * 16, 256), half = align_up(o_status + chunk, 256);
+    return pipeline_host_range(ctx, d, begin, end, chunk, half, counts, "host roundtrip", [&](const ChunkIO& io) {
+        cudaError_t e = cudaMemcpyAsync(io.stage, words + io.at * 16, io.items * 16, cudaMemcpyHostToDevice, io.stream);
+        if (e != cudaSuccess) return e;
+        launch_roundtrip(d, io.stream, (const uint4*)io.stage, io.items, io.stage + o_status, io.counters);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(status + io.at, io.stage + o_status, io.items, cudaMemcpyDeviceToHost, io.stream);
+        return e;
+    });
 }
 
 // Runs fn(device index) for every device of the context on its own host thread and merges
@@ -972,27 +1018,17 @@ extern "C" int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, ui
     if (rc) return rc;
     std::lock_guard<std::mutex> lock(d->stage_mu);
     CU_TRY(ctx, cudaSetDevice(d->device));
-    const uint64_t chunk = std::min<uint64_t>(kChunkWords, n);
-    const uint64_t o_form = align_up(chunk * 16, 256), o_slots = o_form + align_up(chunk * 2, 256);
-    const uint64_t o_ctrl = o_slots + chunk * 32, total = o_ctrl + chunk * 4;
-    rc = ensure_stage(ctx, d, total);
-    if (rc) return rc;
-    uint8_t* st = (uint8_t*)d->stage;
-    for (uint64_t at = 0; at < n; at += chunk) {
-        const uint64_t m = std::min(chunk, n - at);
-        synth_kernel<<<grid_for(d, m), kBlock, 0, d->stream>>>(d->view, g, first + at, m, (uint4*)st, (uint16_t*)(st + o_form),
-                                                                (uint32_t*)(st + o_slots), chunk, (uint32_t*)(st + o_ctrl));
-        CU_TRY(ctx, cudaGetLastError());
-        if (words) CU_TRY(ctx, cudaMemcpyAsync((uint8_t*)words + at * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
-        if (form) CU_TRY(ctx, cudaMemcpyAsync(form + at, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
-        if (slots)
-            for (int k = 0; k < 8; ++k)
-                CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)k * n + at, st + o_slots + (uint64_t)k * chunk * 4, m * 4,
-                                            cudaMemcpyDeviceToHost, d->stream));
-        if (ctrl) CU_TRY(ctx, cudaMemcpyAsync(ctrl + at, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
-    }
-    return CUBIT_OK;
+    const RecordStage L(n);
+    return pipeline_host_range(ctx, d, 0, n, L.chunk, L.half, nullptr, "host stream generator", [&](const ChunkIO& io) {
+        synth_kernel<<<grid_for(d, io.items), kBlock, 0, io.stream>>>(d->view, g, first + io.at, io.items, (uint4*)io.stage,
+                                                                       (uint16_t*)(io.stage + L.o_form), (uint32_t*)(io.stage + L.o_slots),
+                                                                       L.chunk, (uint32_t*)(io.stage + L.o_ctrl));
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess && words)
+            e = cudaMemcpyAsync((uint8_t*)words + io.at * 16, io.stage, io.items * 16, cudaMemcpyDeviceToHost, io.stream);
+        if (e == cudaSuccess) e = records_to_host(L, io, io.at, n, form, slots, ctrl);
+        return e;
+    });
 } catch (...) {
     return translate_exception(ctx);
 }
@@ -1010,32 +1046,42 @@ extern "C" int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const 
     if (n == 0) return CUBIT_OK;
     if (!words || !form || !slots || !ctrl) return fail(ctx, CUBIT_ERR_INVALID, "null buffer");
     DeviceState* d = ctx->devs[(size_t)device_slot].get();
-    std::lock_guard<std::mutex> lock(d->stage_mu);   // one user of the scratch array and of the stream at a time
+    if (d->device < 0 || d->device >= kMaxStaticDevices)
+        return fail(ctx, CUBIT_ERR_INVALID, "device ordinal beyond what the built-in scratch is tracked for");
+    // The array exists once per GPU for the whole process, whatever the number of contexts: its
+    // lock is per device ordinal.  The context's staging lock guards the stream used below.
+    std::lock_guard<std::mutex> scratch_lock(g_static_mu[d->device]);
+    std::lock_guard<std::mutex> lock(d->stage_mu);
     CU_TRY(ctx, cudaSetDevice(d->device));
-    {
+    if (!g_static_addr[d->device]) {
         // One-time set-up per device, with that device current: the symbol's address there.
-        std::lock_guard<std::mutex> g(d->mu);
-        if (!d->static_scratch) {
-            unsigned char* p = nullptr;
-            CU_TRY(ctx, cudaGetSymbolAddress((void**)&p, g_static_scratch));
-            d->static_scratch = p;
-        }
+        unsigned char* p = nullptr;
+        CU_TRY(ctx, cudaGetSymbolAddress((void**)&p, g_static_scratch));
+        g_static_addr[d->device] = p;
     }
-    unsigned char* st = d->static_scratch;
+    unsigned char* st = g_static_addr[d->device];
     unsigned long long* dc = (unsigned long long*)(st + kStaticCountersOff);
     unsigned long long host_counts[CNT_WORDS] = {0, 0, 0, 0, 0};
     // The array keeps what the previous call left: the counters are accumulated into, so they
     // are cleared; the record planes are fully overwritten for the first n entries.
-    CU_TRY(ctx, cudaMemsetAsync(dc, 0, sizeof host_counts, d->stream));
-    CU_TRY(ctx, cudaMemcpyAsync(st, words, n * 16, cudaMemcpyHostToDevice, d->stream));
-    launch_decode(d, d->stream, (const uint4*)st, n, (uint16_t*)(st + kStaticFormOff), (uint32_t*)(st + kStaticSlotsOff), n,
-                  (uint32_t*)(st + kStaticCtrlOff), dc);
-    CU_TRY(ctx, cudaGetLastError());
-    CU_TRY(ctx, cudaMemcpyAsync(form, st + kStaticFormOff, n * 2, cudaMemcpyDeviceToHost, d->stream));
-    CU_TRY(ctx, cudaMemcpyAsync(slots, st + kStaticSlotsOff, n * 32, cudaMemcpyDeviceToHost, d->stream));
-    CU_TRY(ctx, cudaMemcpyAsync(ctrl, st + kStaticCtrlOff, n * 4, cudaMemcpyDeviceToHost, d->stream));
-    CU_TRY(ctx, cudaMemcpyAsync(host_counts, dc, sizeof host_counts, cudaMemcpyDeviceToHost, d->stream));
-    CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+    cudaError_t e = cudaMemsetAsync(dc, 0, sizeof host_counts, d->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(st, words, n * 16, cudaMemcpyHostToDevice, d->stream);
+    if (e == cudaSuccess) {
+        launch_decode(d, d->stream, (const uint4*)st, n, (uint16_t*)(st + kStaticFormOff), (uint32_t*)(st + kStaticSlotsOff), n,
+                      (uint32_t*)(st + kStaticCtrlOff), dc);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(form, st + kStaticFormOff, n * 2, cudaMemcpyDeviceToHost, d->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(slots, st + kStaticSlotsOff, n * 32, cudaMemcpyDeviceToHost, d->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ctrl, st + kStaticCtrlOff, n * 4, cudaMemcpyDeviceToHost, d->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_counts, dc, sizeof host_counts, cudaMemcpyDeviceToHost, d->stream);
+    // Also after an error: copies already queued may still be writing into the caller's buffers or host_counts.
+    const cudaError_t waited = cudaStreamSynchronize(d->stream);
+    if (e == cudaSuccess) e = waited;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, CUBIT_ERR_CUDA, std::string("static decode: ") + cudaGetErrorString(e));
+    }
     if (counts) add_counts(counts, host_counts);
     return CUBIT_OK;
 } catch (...) {
@@ -1121,8 +1167,8 @@ extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint
     if (capacity < total) return fail(ctx, CUBIT_ERR_INVALID, "output capacity below the number of words");
     if (total == 0) return CUBIT_OK;
 
-    // Shard records over devices by cumulative word count; each device gathers its part of
-    // the text ranges into one contiguous staging buffer and decodes it in a single launch.
+    // Shard records over devices by cumulative word count.  The number of launches depends on the
+    // number of words only (one per 4 Mi words of a device's share), never on the number of kernels.
     const size_t g = ctx->devs.size();
     return for_each_device(ctx, counts, [&](size_t k, cubit_counts* part) {
         uint64_t b, e;
@@ -1131,31 +1177,26 @@ extern "C" int cubit_decode_elf(cubit_ctx* ctx, const cubit_elf* elf, const uint
         DeviceState* d = ctx->devs[k].get();
         std::lock_guard<std::mutex> lock(d->stage_mu);
         CU_TRY(ctx, cudaSetDevice(d->device));
-        const uint64_t m = e - b;
-        const uint64_t o_form = align_up(m * 16, 256), o_slots = o_form + align_up(m * 2, 256);
-        const uint64_t o_ctrl = o_slots + m * 32, bytes = o_ctrl + m * 4;
-        int rc = ensure_stage(ctx, d, bytes);
-        if (rc) return rc;
-        uint8_t* st = (uint8_t*)d->stage;
-        for (const Range& r : ranges) {
-            const uint64_t lo = std::max(b, r.rec), hi = std::min(e, r.rec + r.words);
-            if (lo >= hi) continue;
-            const uint8_t* src = elf->bytes + r.file_off + (lo - r.rec) * 16;
-            CU_TRY(ctx, cudaMemcpyAsync(st + (lo - b) * 16, src, (hi - lo) * 16, cudaMemcpyHostToDevice, d->stream));
-        }
-        rc = run_counted(ctx, d, d->stream, part, [&](unsigned long long* dc) {
-            launch_decode(d, d->stream, (const uint4*)st, m, (uint16_t*)(st + o_form), (uint32_t*)(st + o_slots), m,
-                          (uint32_t*)(st + o_ctrl), dc);
+        // The device's share of the records goes through the staging area chunk by chunk: each chunk gathers
+        // its part of the text ranges, is decoded by one launch and copied out while the next one comes in.
+        const RecordStage L(e - b);
+        return pipeline_host_range(ctx, d, b, e, L.chunk, L.half, part, "cubin decode", [&](const ChunkIO& io) {
+            cudaError_t err = cudaSuccess;
+            for (const Range& r : ranges) {
+                const uint64_t lo = std::max(io.at, r.rec), hi = std::min(io.at + io.items, r.rec + r.words);
+                if (lo >= hi) continue;
+                const uint8_t* src = elf->bytes + r.file_off + (lo - r.rec) * 16;
+                err = cudaMemcpyAsync(io.stage + (lo - io.at) * 16, src, (hi - lo) * 16, cudaMemcpyHostToDevice, io.stream);
+                if (err != cudaSuccess) return err;
+            }
+            launch_decode(d, io.stream, (const uint4*)io.stage, io.items, (uint16_t*)(io.stage + L.o_form),
+                          (uint32_t*)(io.stage + L.o_slots), L.chunk, (uint32_t*)(io.stage + L.o_ctrl), io.counters);
+            err = cudaGetLastError();
+            if (err == cudaSuccess) err = records_to_host(L, io, io.at, capacity, form, slots, ctrl);
+            if (err == cudaSuccess && raw_words)
+                err = cudaMemcpyAsync((uint8_t*)raw_words + io.at * 16, io.stage, io.items * 16, cudaMemcpyDeviceToHost, io.stream);
+            return err;
         });
-        if (rc) return rc;
-        CU_TRY(ctx, cudaMemcpyAsync(form + b, st + o_form, m * 2, cudaMemcpyDeviceToHost, d->stream));
-        for (int s = 0; s < 8; ++s)
-            CU_TRY(ctx, cudaMemcpyAsync(slots + (uint64_t)s * capacity + b, st + o_slots + (uint64_t)s * m * 4, m * 4,
-                                        cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(ctrl + b, st + o_ctrl, m * 4, cudaMemcpyDeviceToHost, d->stream));
-        if (raw_words) CU_TRY(ctx, cudaMemcpyAsync((uint8_t*)raw_words + b * 16, st, m * 16, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
-        return (int)CUBIT_OK;
     });
 } catch (...) {
     return translate_exception(ctx);
@@ -1199,9 +1240,9 @@ extern "C" int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, con
         if (rc) return rc;
         uint8_t* st = (uint8_t*)d->stage;
         for (const Range& r : ranges)
-            CU_TRY(ctx, cudaMemcpyAsync(st + r.rec * 16, elf->bytes + r.file_off, r.words * 16, cudaMemcpyHostToDevice, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(st + o_start, start.data(), (n_sections + 1) * 8, cudaMemcpyHostToDevice, d->stream));
-        CU_TRY(ctx, cudaMemsetAsync(st + o_max, 0, o_flag - o_max, d->stream));
+            CU_TRY_DRAIN(ctx, d->stream, cudaMemcpyAsync(st + r.rec * 16, elf->bytes + r.file_off, r.words * 16, cudaMemcpyHostToDevice, d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaMemcpyAsync(st + o_start, start.data(), (n_sections + 1) * 8, cudaMemcpyHostToDevice, d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaMemsetAsync(st + o_max, 0, o_flag - o_max, d->stream));
         if (use_shared(d, total))
             meta_kernel<HotShared><<<grid_shared(d, total), kBlockShared, d->hot_bytes, d->stream>>>(
                 d->view, (const uint4*)st, total, (const uint64_t*)(st + o_start), n_sections, (uint32_t*)(st + o_max),
@@ -1210,11 +1251,11 @@ extern "C" int cubit_infer_kernel_meta(cubit_ctx* ctx, const cubit_elf* elf, con
             meta_kernel<HotGlobal><<<grid_for(d, total), kBlock, 0, d->stream>>>(
                 d->view, (const uint4*)st, total, (const uint64_t*)(st + o_start), n_sections, (uint32_t*)(st + o_max),
                 (uint32_t*)(st + o_bar), st + o_flag);
-        CU_TRY(ctx, cudaGetLastError());
-        CU_TRY(ctx, cudaMemcpyAsync(max_reg.data(), st + o_max, n_sections * 4, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(barriers.data(), st + o_bar, n_sections * 4, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaMemcpyAsync(flags.data(), st + o_flag, total, cudaMemcpyDeviceToHost, d->stream));
-        CU_TRY(ctx, cudaStreamSynchronize(d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaGetLastError());
+        CU_TRY_DRAIN(ctx, d->stream, cudaMemcpyAsync(max_reg.data(), st + o_max, n_sections * 4, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaMemcpyAsync(barriers.data(), st + o_bar, n_sections * 4, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaMemcpyAsync(flags.data(), st + o_flag, total, cudaMemcpyDeviceToHost, d->stream));
+        CU_TRY_DRAIN(ctx, d->stream, cudaStreamSynchronize(d->stream));
     }
     uint64_t ne = 0;
     for (uint32_t k = 0; k < n_sections; ++k) {

@@ -83,14 +83,20 @@ std::vector<uint8_t> elf_patch_text(const uint8_t* bytes, uint64_t len, uint32_t
     uint8_t* b = out.data();
     const uint64_t n = out.size();
     auto moved = [&](uint64_t v) { return (uint64_t)((int64_t)v + delta); };
+    // [at, at + size) lies inside the image; written so that no sum can wrap.
+    auto inside = [&](uint64_t at, uint64_t size) { return at <= n && size <= n - at; };
+    if (n < 0x40) return out;
     if (rd64(b + 0x28) > start) wr64(b + 0x28, moved(rd64(b + 0x28)));
     if (rd64(b + 0x20) > start) wr64(b + 0x20, moved(rd64(b + 0x20)));
     const uint64_t shoff = rd64(b + 0x28), shnum = rd16(b + 0x3C), phoff = rd64(b + 0x20), phnum = rd16(b + 0x38);
+    // A header table that starts outside the image cannot be fixed up.
+    if ((phnum && phoff > n) || (shnum && shoff > n))
+        throw std::runtime_error("failed to parse ELF: header table offset past end of file");
     for (uint64_t p = 0; p < phnum; ++p) {
+        if (!inside(phoff, 56) || p > (n - phoff - 56) / 56) break;
         const uint64_t ph = phoff + p * 56;
-        if (ph + 56 > n) break;
         const uint64_t p_offset = rd64(b + ph + 8), p_filesz = rd64(b + ph + 0x20);
-        if (p_offset <= start && start < p_offset + p_filesz) {
+        if (p_offset <= start && start - p_offset < p_filesz) {
             wr64(b + ph + 0x20, moved(p_filesz));
             wr64(b + ph + 0x28, moved(rd64(b + ph + 0x28)));
         } else if (p_offset > start) {
@@ -99,29 +105,30 @@ std::vector<uint8_t> elf_patch_text(const uint8_t* bytes, uint64_t len, uint32_t
     }
     int64_t text_shndx = -1;
     for (uint64_t s = 0; s < shnum; ++s) {
+        if (!inside(shoff, 64) || s > (n - shoff - 64) / 64) break;
         const uint64_t sh = shoff + s * 64;
-        if (sh + 64 > n) break;
         const uint64_t sh_offset = rd64(b + sh + 0x18), sh_size = rd64(b + sh + 0x20);
         if (sh_offset == start && sh_size == old_size) { wr64(b + sh + 0x20, code_len); text_shndx = (int64_t)s; }
         else if (sh_offset > start) wr64(b + sh + 0x18, moved(sh_offset));
     }
     if (text_shndx >= 0)
         for (uint64_t s = 0; s < shnum; ++s) {
+            if (!inside(shoff, 64) || s > (n - shoff - 64) / 64) break;
             const uint64_t sh = shoff + s * 64;
-            if (sh + 64 > n) break;
             if (rd32(b + sh + 4) != SHT_SYMTAB) continue;
             const uint64_t sym_off = rd64(b + sh + 0x18), sym_total = rd64(b + sh + 0x20);
+            if (sym_total >= 24 && sym_off > n) throw std::runtime_error("failed to parse ELF: symbol table offset past end of file");
             for (uint64_t i = 0; i < sym_total / 24; ++i) {
+                if (!inside(sym_off, 24) || i > (n - sym_off - 24) / 24) break;
                 const uint64_t so = sym_off + i * 24;
-                if (so + 24 > n) break;
                 if (rd16(b + so + 6) == (uint64_t)text_shndx && (b[so + 4] >> 4) >= 1) wr64(b + so + 16, code_len);
             }
             break;   // the first symbol table only
         }
     // The first section that starts with a DWARF64 length marker is taken to be .debug_frame.
     for (uint64_t s = 0; s < shnum; ++s) {
+        if (!inside(shoff, 64) || s > (n - shoff - 64) / 64) break;
         const uint64_t sh = shoff + s * 64;
-        if (sh + 64 > n) break;
         const uint64_t sh_offset = rd64(b + sh + 0x18), sh_size = rd64(b + sh + 0x20);
         if (sh_size < 48 || sh_offset > n || sh_size > n - sh_offset) continue;
         if (rd32(b + sh_offset) != 0xFFFFFFFFu) continue;

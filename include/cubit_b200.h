@@ -161,10 +161,13 @@ int cubit_synth_batch(cubit_ctx* ctx, uint32_t mix, uint64_t seed, uint32_t nois
  *   - device_slot picks one of the context's devices by position in the list given to
  *     cubit_ctx_create.  The first call on a device looks up the array's address there
  *     (a one-time set-up); make that first call before starting any stream capture.
- *   - All calls on one device share the array.  It keeps the previous call's contents; the
- *     entry point clears the counters it accumulates into and overwrites the rest.  Calls that
- *     overlap in time on the same device (also with the CUBIT_MEM_HOST paths, which share the
- *     device's staging stream) are serialised inside the library by a per-device lock.
+ *   - All calls on one GPU share the array, whichever context they come from: it exists once
+ *     per GPU and process.  It keeps the previous call's contents; the entry point clears the
+ *     counters it accumulates into and overwrites the rest.  Calls that overlap in time on the
+ *     same GPU would race on it, so the library serialises them with one lock per GPU that all
+ *     contexts of the process share (and, within a context, with the CUBIT_MEM_HOST paths,
+ *     which use the same staging stream).  Another process, or another copy of the library
+ *     loaded into this one, has an array of its own.
  * The call returns when the results are in the host buffers. */
 int cubit_decode_batch_static(cubit_ctx* ctx, int device_slot, const void* words, uint64_t n, uint16_t* form,
                               uint32_t* slots, uint32_t* ctrl, cubit_counts* counts);

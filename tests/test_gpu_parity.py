@@ -81,14 +81,37 @@ def adversarial_words(rng, per_variant):
     return words_from_ints(out)
 
 
-def test_adversarial_words(codec, oracle):
-    words = adversarial_words(np.random.default_rng(1), 40)
+# Batches of at least this many words run on the kernels that stage the table in shared memory
+# (the ones the benchmark times); smaller ones on the kernels that read it through global memory.
+STAGED_MIN_WORDS = 1 << 17
+
+
+@pytest.mark.parametrize("per_variant", [48, 12])
+def test_adversarial_words(codec, oracle, per_variant):
+    """The real table's edge words through both kernel flavours: 48 per variant is 137,856 words (staged table),
+    12 per variant 34,464 (table in global memory)."""
+    words = adversarial_words(np.random.default_rng(1), per_variant)
+    assert (len(words) >= STAGED_MIN_WORDS) == (per_variant == 48)
     d = codec.decode_batch(words)
     od = oracle.decode_batch(words, threads=T)
     assert_records_equal(d[:3], od)
     assert (codec.encode_batch(*d[:3]) == oracle.encode_batch(*od, threads=T)).all()
     status, _ = codec.roundtrip_batch(words)
     assert (status == oracle.roundtrip_batch(words, threads=T)).all()
+
+
+def test_wide_index_kernels_agree(oracle, monkeypatch):
+    """Batches of 2^31 words and more use 64-bit word indices in the decode kernel; CUBIT_WIDE_INDEX=1 selects
+    those kernels at any size so that they can be compared with the oracle here."""
+    monkeypatch.setenv("CUBIT_WIDE_INDEX", "1")
+    wide = cubit_b200.Codec(devices=(0,))
+    try:
+        for n in (STAGED_MIN_WORDS + 4099, 5000):
+            words = oracle.synth(MIX_UNIFORM, 31, n, noise_ppm=50000, records=False, threads=T)
+            got = wide.decode_batch(words)
+            assert_records_equal(got[:3], oracle.decode_batch(words, threads=T))
+    finally:
+        wide.close()
 
 
 def test_uniform_random_words_are_rejected_like_the_oracle(codec, oracle):
@@ -163,11 +186,12 @@ def test_python_decode_matches_oracle_fields(codec, oracle):
         del synth
 
 
-def test_device_pointer_path(codec, oracle):
-    """Buffers in device memory, kernel queued on a caller stream (torch is only the allocator here)."""
+@pytest.mark.parametrize("n", [STAGED_MIN_WORDS + 20003, 100003])
+def test_device_pointer_path(codec, oracle, n):
+    """Buffers in device memory, kernel queued on a caller stream (torch is only the allocator here); once above and
+    once below the batch size from which the kernels stage the table in shared memory."""
     torch = pytest.importorskip("torch")
-    n = 100003
-    words = oracle.synth(MIX_ZIPF, 5, n, noise_ppm=10000, records=False)
+    words = oracle.synth(MIX_ZIPF, 5, n, noise_ppm=10000, records=False, threads=T)
     dev = torch.device("cuda", 0)
     dw = torch.from_numpy(words.reshape(-1)).to(dev)
     form = torch.empty(n, dtype=torch.int16, device=dev)

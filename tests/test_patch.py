@@ -97,6 +97,27 @@ def test_patch_text_errors():
         cubit_b200.patch_text(b"not an elf", 0, b"")
 
 
+@pytest.mark.parametrize("what", ["e_phoff", "e_shoff_after_parse", "symtab_offset"])
+def test_patch_text_rejects_header_offsets_near_2_to_64(what):
+    """Offsets whose sums wrap around 2^64 must end in an error, not in reads or writes outside the image
+    (reference src/elf.rs:109-190 walks the same tables with bounds-checked slices)."""
+    img = bytearray(image())
+    huge = 0xFFFFFFFFFFFFFFF8
+    if what == "e_phoff":
+        struct.pack_into("<Q", img, 0x20, huge)
+        struct.pack_into("<H", img, 0x38, 2)
+    elif what == "symtab_offset":
+        heads = section_headers(bytes(img))
+        shoff, = struct.unpack_from("<Q", img, 0x28)
+        sym = next(i for i, h in enumerate(heads) if h[1] == 2)
+        struct.pack_into("<Q", img, shoff + 64 * sym + 0x18, huge)
+    else:
+        # the section table itself is read by the parser first: a bad e_shoff never reaches the splice
+        struct.pack_into("<Q", img, 0x28, huge)
+    with pytest.raises((cubit_b200.CubitError, OSError), match="ELF|load error"):
+        cubit_b200.patch_text(bytes(img), 1, bytes(16 * 5))
+
+
 @pytest.mark.gpu
 def test_patch_keeps_faithful_words_and_high_halves(codec, oracle):
     import json

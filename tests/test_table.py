@@ -128,3 +128,14 @@ def test_cubit_table_env_is_strict(tmp_path, monkeypatch):
     good.write_text(flat_table('{"and_base":"0x1","fields":[]}'))
     monkeypatch.setenv("CUBIT_TABLE", str(good))
     assert Codec(devices=(), table_path=TABLE).table_info() == (1, 1)   # the variable wins over the argument
+
+
+def test_the_reference_module_name_is_importable():
+    """`import cubit` is what a user of the reference writes (reference src/python.rs:215-225)."""
+    import cubit
+    assert cubit.table_info() == (2001, 2872)
+    assert sorted(cubit.__all__) == sorted(["encode", "decode", "decode_kernel", "table_info", "to_sass", "asm"])
+    for name in cubit.__all__:
+        assert callable(getattr(cubit, name))
+    with pytest.raises(NotImplementedError):
+        cubit.asm("NOP")
