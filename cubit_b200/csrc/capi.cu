@@ -327,6 +327,11 @@ struct cubit_ctx {
     std::mutex err_mu;
     std::map<std::thread::id, std::string> errors;
     std::mutex synth_mu;
+    // Host-side fault injection for tests (read from the environment when the context is made):
+    // CUBIT_TEST_FAIL_SLOT=k makes the worker of device slot k report a failure instead of running,
+    // CUBIT_TEST_FAIL_ALLOC=1 makes every growth of a staging buffer fail.  Nothing on a GPU is faulted.
+    int test_fail_slot = -1;
+    bool test_fail_alloc = false;
     std::unique_ptr<TextEncoder> text;   // built with the context; reads `table`
     std::vector<VariantPrintCache> print_cache;   // per variant, for the printer
 };
@@ -568,6 +573,7 @@ int run_counted(cubit_ctx* ctx, DeviceState* d, cudaStream_t stream, cubit_count
 
 int ensure_stage(cubit_ctx* ctx, DeviceState* d, uint64_t bytes) {
     if (d->stage_bytes >= bytes) return CUBIT_OK;
+    if (ctx->test_fail_alloc) return fail(ctx, CUBIT_ERR_NOMEM, "staging buffer allocation failed (injected by CUBIT_TEST_FAIL_ALLOC)");
     if (d->stage) { CU_TRY(ctx, cudaFree(d->stage)); d->stage = nullptr; d->stage_bytes = 0; }
     CU_TRY(ctx, cudaMalloc(&d->stage, bytes));
     d->stage_bytes = bytes;
@@ -726,7 +732,10 @@ int for_each_device(cubit_ctx* ctx, cubit_counts* counts, Fn fn) {
     std::vector<std::string> messages(g);
     memset(partial.data(), 0, g * sizeof(cubit_counts));
     auto body = [&](size_t k) {
-        rcs[k] = fn(k, counts ? &partial[k] : nullptr);
+        if (ctx->test_fail_slot == (int)k)
+            rcs[k] = fail(ctx, CUBIT_ERR_CUDA, "device slot " + std::to_string(k) + " failed (injected by CUBIT_TEST_FAIL_SLOT)");
+        else
+            rcs[k] = fn(k, counts ? &partial[k] : nullptr);
         if (rcs[k]) messages[k] = cubit_last_error(ctx);
         if (g > 1) {   // a worker thread ends here: its message slot goes with it
             std::lock_guard<std::mutex> lock(ctx->err_mu);
@@ -798,6 +807,8 @@ extern "C" int cubit_ctx_create(const char* table_path, const int* devices, int 
         return fail(nullptr, CUBIT_ERR_TABLE, std::string("table ") + path + ": " + e.what());
     }
     const FlatTable& ft = ctx->flat;
+    if (const char* slot = getenv("CUBIT_TEST_FAIL_SLOT")) ctx->test_fail_slot = *slot ? atoi(slot) : -1;
+    if (const char* alloc = getenv("CUBIT_TEST_FAIL_ALLOC")) ctx->test_fail_alloc = alloc[0] == '1';
     ctx->text.reset(new TextEncoder(ctx->table));
     for (const VariantMeta& m : ft.meta) ctx->print_cache.push_back(make_print_cache(m.key, m.opcode, m.mod_group));
     ctx->field_infos.resize(ft.meta.size());

@@ -434,6 +434,17 @@ def test_large_host_batch_crosses_chunk_and_stream_boundaries(codec, oracle):
     status, rc = codec.roundtrip_batch(words)
     assert (status[idx] == oracle.roundtrip_batch(words[idx], threads=T)).all()
     assert rc["n_rejected"] == counts["n_rejected"] and rc["n_exact"] + rc["n_mismatch"] == counts["n_decoded"]
+    # a cubin whose text crosses the chunk boundaries too: kernels of uneven length cut from the same words
+    cuts = [0, 1000003, 1000003 + 2500007, 5 * 1024 * 1024 + 77, n - n % 8]
+    image = cubit_b200.build_cubin([(f"k{k}", words[cuts[k]:cuts[k + 1]].tobytes()) for k in range(4)])
+    sections, word_start, eform, eslots, ectrl, raw, ecounts = codec.decode_elf(image)
+    assert len(sections) == 4 and int(word_start[-1]) == len(raw) >= cuts[-1]
+    again = codec.decode_batch(raw)
+    assert (eform == again[0]).all() and (eslots == again[1]).all() and (ectrl == again[2]).all() and ecounts == again[3]
+    for k in range(4):                                   # each section starts with its kernel's words
+        at, m = int(word_start[k]), cuts[k + 1] - cuts[k]
+        assert (raw[at:at + m] == words[cuts[k]:cuts[k + 1]]).all()
+        assert (eform[at:at + m] == form[cuts[k]:cuts[k + 1]]).all()
 
 
 def test_infer_kernel_meta_matches_the_reference_algorithm(codec, oracle):
@@ -459,3 +470,40 @@ def test_infer_kernel_meta_matches_the_reference_algorithm(codec, oracle):
     assert len(one) == 1 and one[0] == got[4]
     with pytest.raises(ValueError, match="not found"):
         codec.infer_kernel_meta(image, "zzz")
+
+
+def test_host_injected_failures_come_back_as_errors(oracle, monkeypatch):
+    """Failures made on the host (nothing on the GPU is faulted): a device worker that reports an error instead of
+    running, and a staging buffer that cannot grow.  Each must come back as a return code with a message, leave
+    nothing running, and leave the library usable: the next context works."""
+    words = oracle.synth(MIX_ZIPF, 41, 50000, records=False, threads=T)
+    want = oracle.decode_batch(words, threads=T)
+    monkeypatch.setenv("CUBIT_TEST_FAIL_SLOT", "0")
+    broken = cubit_b200.Codec(devices=(0,))
+    monkeypatch.delenv("CUBIT_TEST_FAIL_SLOT")
+    for call in (lambda: broken.decode_batch(words), lambda: broken.roundtrip_batch(words), lambda: broken.encode_batch(*want)):
+        with pytest.raises(cubit_b200.CubitError) as e:
+            call()
+        assert e.value.code == -3 and "device slot 0 failed" in e.value.message
+    broken.close()
+    monkeypatch.setenv("CUBIT_TEST_FAIL_ALLOC", "1")
+    starved = cubit_b200.Codec(devices=(0,))
+    monkeypatch.delenv("CUBIT_TEST_FAIL_ALLOC")
+    with pytest.raises(cubit_b200.CubitError) as e:
+        starved.decode_batch(words)
+    assert e.value.code == -7 and "allocation failed" in e.value.message
+    # the paths that need no staging buffer still work in that context, and so does the built-in scratch
+    assert_records_equal(starved.decode_batch_static(words)[:3], want)
+    starved.close()
+    healthy = cubit_b200.Codec(devices=(0,))
+    assert_records_equal(healthy.decode_batch(words)[:3], want)
+    healthy.close()
+
+
+def test_the_reference_module_name_decodes_and_encodes(codec):
+    """`import cubit` (reference src/python.rs:215-225) on the GPU: decode, to_sass and encode agree with the Codec."""
+    import cubit
+    lo, hi = codec.encode("IADD3 R5, PT, PT, R9, R4, R5")
+    assert cubit.encode("IADD3 R5, PT, PT, R9, R4, R5") == (lo, hi)
+    assert cubit.decode(lo, hi) == codec.decode(lo, hi)
+    assert cubit.to_sass(lo, hi) == "IADD3 R5, PT, PT, R9, R4, R5"
