@@ -94,10 +94,21 @@ def main(ref_root: str) -> None:
             raise SystemExit(f"src/elf_builder.rs:{first} does not hold a 16-byte array any more")
         pad.append({"source": f"src/elf_builder.rs:{first}", "name": name, "key": key,
                     "word": "0x%032x" % int.from_bytes(bytes(bytes_), "little")})
+    # Key splitting vectors of the printer's own unit tests (src/printer.rs:1414-1440): for each test the key is on
+    # the first line given, the expected opcode on the next and the operand kinds on the one after.
+    prn = (ref / "src" / "printer.rs").read_text().splitlines()
+    printer_keys = []
+    for first in (1416, 1423, 1430, 1437):
+        key = re.search(r'parse_ins_key\("([^"]+)"\)', prn[first - 1])
+        op = re.search(r'assert_eq!\(op, "([^"]+)"\)', prn[first])
+        ops = re.findall(r'"([^"]+)"', prn[first + 1])
+        if not key or not op or not ops:
+            raise SystemExit(f"src/printer.rs:{first} no longer holds a parse_ins_key test")
+        printer_keys.append({"source": f"src/printer.rs:{first}", "key": key.group(1), "opcode": op.group(1), "operands": ops})
     table = json.loads((ref / "tables" / "SM120_SOURCE.json").read_text())
     out = {"reference": "kacper-daftcode/cubit", "table_sha256": table["sha256"],
            "instruction_forms": table["instruction_forms"], "encoding_variants": table["encoding_variants"],
-           "sched_mask": "0x%032x" % (0x1FFFF << 105), "cases": cases, "padding_words": pad,
+           "sched_mask": "0x%032x" % (0x1FFFF << 105), "cases": cases, "padding_words": pad, "printer_keys": printer_keys,
            "ctrl_strings": ["B--2---:R0:W1:-:S07", "B01--4-:R-:W-:-:S05", "B------:R-:W-:-:S01", "B0----5:R0:W5:Y:S05"]}
     dest = Path(__file__).with_name("encoding_words.json")
     dest.write_text(json.dumps(out, indent=1) + "\n")

@@ -191,6 +191,21 @@ def test_printer_reference_vectors_cpu(host_codec, oracle):
         assert cpu_encode(host_codec, oracle, case["sass"])[0] & ~SCHED_MASK == w & ~SCHED_MASK
 
 
+def test_printer_key_vectors_of_the_reference(host_codec):
+    """The printer's own unit vectors (reference src/printer.rs:1414-1440): a key splits into the opcode and the
+    operand kinds that the printer walks.  The library keeps the opcode per variant; the operand kinds are what
+    is left of the key."""
+    assert len(GOLDEN["printer_keys"]) == 4
+    for case in GOLDEN["printer_keys"]:
+        key = case["key"]
+        variants = [v for v in range(host_codec.table_info()[1]) if host_codec.variant(v).key == key]
+        assert variants, key
+        for v in variants:
+            m = host_codec.variant(v)
+            assert m.opcode == case["opcode"], case
+            assert m.key[len(m.opcode) + 1:].split("_") == case["operands"], case
+
+
 def test_printer_formats_cpu(host_codec, oracle):
     enc = lambda s, a=0: cpu_encode(host_codec, oracle, s, a)[0]
     show = lambda s, a=0: cpu_print(host_codec, oracle, enc(s, a), a)
