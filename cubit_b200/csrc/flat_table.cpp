@@ -229,6 +229,7 @@ struct TreeBuilder {
         };
         std::vector<uint32_t> leaf_group(order.size()), leaf_key(order.size()), leaf_within(order.size());
         uint32_t leaf_broad16 = 0;   // which of the first 16 classes have a broad record
+        bool leaf_has_broad = false;
         for (size_t ci = 0; ci < order.size(); ++ci) {
             const ClassKey& ck = order[ci];
             std::vector<uint32_t>& mem = groups[ck];
@@ -239,11 +240,16 @@ struct TreeBuilder {
             const Static& best = st[mem[0]];
             uint32_t rec[CR_WORDS] = {0};
             for (int k = 0; k < 3; ++k) {
-                // A side that can never match gets mask 0 / base 1: (cc & 0) ^ 1 is never 0.
+                // A side that can never match gets mask 0 / base bit 16: (cc & 0) ^ base is never 0.  Bits 15:0
+                // of limb 0 are not part of the test (the word's are cleared first): bits 11:0 chose the directory
+                // entry, bits 15:12 are the guard, which no mask holds.
                 rec[CR_SMASK + k] = best.s_ok ? uint32_t(best.smask >> (32 * k)) : 0;
-                rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 1u : 0u);
+                rec[CR_SBASE + k] = best.s_ok ? uint32_t(best.sbase >> (32 * k)) : (k == 0 ? 0x10000u : 0u);
                 rec[CR_BASE + k] = uint32_t(best.base96 >> (32 * k));
             }
+            if (rec[CR_SMASK] & 0xF000u) throw std::runtime_error("internal: a strict mask holds guard bits");
+            rec[CR_SMASK] &= 0xFFFF0000u;
+            rec[CR_SBASE] &= 0xFFFF0000u;
             uint32_t info = mem.size() > 1 ? uint32_t(CI_SEVERAL) : 0u;
             // The broad test only adds something when it can succeed where the strict one fails.
             if (best.b_ok && !(best.s_ok && best.bmask == best.smask)) {
@@ -261,6 +267,8 @@ struct TreeBuilder {
             const bool tie_within = mem.size() > 1 && (key_of[mem[1]] >> KEY_TUPLE_SHIFT) == (key_of[mem[0]] >> KEY_TUPLE_SHIFT);
             rec[CR_INFO] = info;
             rec[CR_GROUP] = group_mask;
+            // Leaves of at most 16 classes keep the best member's output-predicate field mask above the group bits.
+            if (order.size() <= 16) rec[CR_GROUP] |= r2_mask_of(best.flags) & 0xFFFF0000u;
             rec[CR_FIRST_FLAGS] = best.flags;
             rec[CR_KEY] = key_of[mem[0]] | (tie_within ? (uint32_t)KEY_WITHIN : 0u);
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
@@ -283,7 +291,9 @@ struct TreeBuilder {
                 ft.flagbest.insert(ft.flagbest.end(), fb, fb + FB_WORDS);
             }
             rec[CR_ANY_FLAGS] = any;
+            rec[CR_SMASK] |= any;   // the test reads the flags from here
             if (ci < 16 && (info & CI_HAS_BROAD)) leaf_broad16 |= 1u << ci;
+            if (info & CI_HAS_BROAD) leaf_has_broad = true;
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
             leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = tie_within ? 1u : 0u;
         }
@@ -323,9 +333,9 @@ struct TreeBuilder {
                 if (leaf_group[ci] & ~(1u << ci)) any_unsettled = true;
                 if (b.s_ok && ((b.base96 & ~b.smask) & ~guard)) eligible = false;
             }
-            if (eligible && any_unsettled) {
+            // The memo number sits between the group bits and bit 16 of CR_GROUP; leaves beyond that many rank in the loop.
+            if (eligible && any_unsettled && ft.n_memo_leaves + 2 < (1u << (16 - MEMO_MAX_CLASSES))) {
                 const uint32_t id = ft.n_memo_leaves++;
-                if (id + 1 >= (1u << (32 - MEMO_MAX_CLASSES))) throw std::runtime_error("too many memo leaves");
                 ft.memo.resize(size_t(id + 1) * MEMO_BYTES, 0);
                 uint8_t* out = &ft.memo[size_t(id) * MEMO_BYTES];
                 const uint32_t n = uint32_t(order.size());
@@ -352,13 +362,23 @@ struct TreeBuilder {
         }
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
-        return REF_LEAF | first_class | (uint32_t(order.size()) << 20);
+        return REF_LEAF | first_class | (uint32_t(order.size()) << 20) | (leaf_has_broad ? uint32_t(REF_BROAD) : 0u) |
+               (leaf_relevant ? uint32_t(REF_BROAD_ALWAYS) : 0u);
     }
 
     // The node hash before its final shift: one multiplier per limb, summed (three multiply-adds
     // on the device).
     static uint32_t mix(u128 x, const uint32_t m[3]) {
         return uint32_t(x) * m[0] + uint32_t(x >> 32) * m[1] + uint32_t(x >> 64) * m[2];
+    }
+    // Fills node record `node` and returns the ref to it.
+    uint32_t write_node(uint32_t node, u128 mask, const uint32_t m[3], uint32_t child_base, uint32_t shift) {
+        uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
+        n[NR_MASK0] = uint32_t(mask); n[NR_MASK1] = uint32_t(mask >> 32); n[NR_MASK2] = uint32_t(mask >> 64);
+        n[NR_MULT0] = m[0]; n[NR_MULT1] = m[1]; n[NR_MULT2] = m[2];
+        n[NR_CHILD] = child_base;
+        n[NR_SHIFT] = shift;
+        return REF_NODE | node | ((n[NR_MASK0] | n[NR_MASK1]) ? uint32_t(REF_WIDE) : 0u);
     }
     static void draw_multipliers(uint64_t* rng, uint32_t m[3]) {
         for (int k = 0; k < 3; ++k) { *rng = splitmix64(*rng); m[k] = uint32_t(*rng >> 16) | 1u; }
@@ -425,14 +445,7 @@ struct TreeBuilder {
                 ft.children.resize(ft.children.size() + (size_t(1) << kk), REF_LEAF);
                 for (size_t i = 0; i < pattern.size(); ++i)
                     ft.children[child_base + (kk ? mix(pattern[i], m) >> (32 - kk) : 0u)] = target[i];
-                uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
-                for (int q = 0; q < 3; ++q) n[NR_MASK + q] = uint32_t(mask >> (32 * q));
-                n[NR_MULT0] = m[0];
-                n[NR_MULT1] = m[1];
-                n[NR_MULT2] = m[2];
-                n[NR_CHILD] = child_base;
-                n[NR_SHIFT] = 32 - kk;
-                return REF_NODE | node;
+                return write_node(node, mask, m, child_base, 32 - kk);
             }
         }
         throw std::runtime_error("no perfect hash for a bit-node subtree");
@@ -500,14 +513,7 @@ struct TreeBuilder {
                     const uint32_t ref = build(kv.second, used | common, depth + 1);
                     ft.children[child_base + h] = ref;
                 }
-                uint32_t* n = &ft.nodes[size_t(node) * NR_WORDS];
-                for (int k = 0; k < 3; ++k) n[NR_MASK + k] = uint32_t(common >> (32 * k));
-                n[NR_MULT0] = mult[0];
-                n[NR_MULT1] = mult[1];
-                n[NR_MULT2] = mult[2];
-                n[NR_CHILD] = child_base;
-                n[NR_SHIFT] = 32 - bits;
-                return REF_NODE | node;
+                return write_node(node, common, mult, child_base, 32 - bits);
             }
             // No perfect hash found: fall through and scan (still correct).
         }
@@ -719,7 +725,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         // Slots of the fields of limb 0, 1, 2 in the order they are handed out, and the multiplier
         // word (XR_MULT + ...) that serves each (slot, limb) pair.
         static const uint32_t kSlots[3][3] = {{0, 1, 2}, {3, 5, 6}, {4, 6, 5}};
-        static const uint32_t kMultWord[3][3] = {{0, 1, 2}, {3, 5, 7}, {4, 8, 6}};
+        uint32_t limb2_slots = 0;   // slots 5 / 6 taken by a limb 2 field
         uint32_t taken[3] = {0, 0, 0};
         uint32_t amounts[7] = {0, 0, 0, 0, 0, 0, 0};
         const uint32_t gfield_start = uint32_t(ft.gfields.size());
@@ -735,8 +741,10 @@ FlatTable FlatTable::compile(const IsaTable& t) {
                     const uint32_t limb = f.shift >> 5, k = taken[limb]++;
                     const uint32_t slot = kSlots[limb][k];
                     pos = slot * 32;
-                    xr[XR_MULT + kMultWord[limb][k]] = 1u << (32u - (f.shift & 31u) - sb);
+                    xr[XR_MULT + slot] = 1u << (32u - (f.shift & 31u) - sb);
                     amounts[slot] = 32u - sb;
+                    if (limb == 2 && slot == 5) limb2_slots |= XC_SLOT5_LIMB2;
+                    if (limb == 2 && slot == 6) limb2_slots |= XC_SLOT6_LIMB2;
                 }
             }
             FieldMeta fmeta;
@@ -770,7 +778,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         }
         m.synth_mask = synth;
         xr[XR_CFG] = amounts[6] | (rot1 << XC_ROT1_POS) | (rot2 << XC_ROT2_POS) | (uint32_t(m.layout_kind) << XC_LAYOUT_POS) |
-                     (synth << XC_SYNTH_POS);
+                     limb2_slots | (synth << XC_SYNTH_POS);
         {
             std::vector<std::string> parts = split(key, '_');
             int skip = 0;
@@ -907,11 +915,10 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             if ((cfg >> XC_LAYOUT_POS) & 1u) {
                 for (uint32_t k = 0; k < 3; ++k) er[ER_MASK + 3 * k + k] = xr[XR_MASK + k];   // slot k is limb k, in place
             } else {
-                static const uint32_t kMultSlot[XR_N_MULT] = CB_XR_MULT_SLOT, kMultLimb[XR_N_MULT] = CB_XR_MULT_LIMB;
-                for (uint32_t w = 0; w < XR_N_MULT; ++w) {
-                    const uint32_t mult = xr[XR_MULT + w];
+                for (uint32_t s = 0; s < 7; ++s) {
+                    const uint32_t mult = xr[XR_MULT + s];
                     if (!mult) continue;
-                    const uint32_t s = kMultSlot[w], limb = kMultLimb[w];
+                    const uint32_t limb = s < 3 ? 0u : (s == 3 ? 1u : (s == 4 ? 2u : ((cfg & (s == 5 ? XC_SLOT5_LIMB2 : XC_SLOT6_LIMB2)) ? 2u : 1u)));
                     const uint32_t right = ((s < 6 ? xr[XR_AMOUNT] >> (5 * s) : cfg) & 31u), take = 32u - right;
                     const uint32_t sh = 32u - take - uint32_t(__builtin_ctz(mult));
                     const uint32_t ones = take >= 32 ? 0xFFFFFFFFu : ((1u << take) - 1u);
@@ -965,7 +972,7 @@ FlatTable FlatTable::compile(const IsaTable& t) {
         const uint32_t never = uint32_t(ft.classes.size() / CR_WORDS);
         if (never >= (1u << 20)) throw std::runtime_error("match tree too large");
         uint32_t rec[CR_WORDS] = {0};
-        rec[CR_SBASE] = 1;   // (cc & 0) ^ 1 is never 0
+        rec[CR_SBASE] = 0x10000u;   // (cc & 0) ^ base is never 0
         ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
         const uint32_t empty = REF_LEAF, filled = REF_LEAF | never | (1u << 20);
         for (uint32_t& r : dir) if (r == empty) r = filled;
@@ -990,11 +997,20 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     };
     for (size_t q = 0; q < 2; ++q) L.nodes[q] = place(quad_plane(ft.nodes, NR_WORDS, q));
     L.children = place(ft.children);
-    for (size_t q = 0; q < 3; ++q) L.classes[q] = place(quad_plane(ft.classes, CR_WORDS, q));
+    // Words [first, first + count) of every record of a section whose records are `words` wide.
+    auto word_plane = [](const std::vector<uint32_t>& src, size_t words, size_t first, size_t count) {
+        std::vector<uint32_t> out;
+        for (size_t r = 0; r * words < src.size(); ++r) out.insert(out.end(), src.begin() + r * words + first, src.begin() + r * words + first + count);
+        return out;
+    };
+    L.classes[0] = place(word_plane(ft.classes, CR_WORDS, CR_SMASK, 4));       // mask[3], base[0]
+    L.classes[1] = place(word_plane(ft.classes, CR_WORDS, CR_SBASE + 1, 2));   // base[1], base[2]
+    L.classes[2] = place(quad_plane(ft.classes, CR_WORDS, 2));
+    L.class_info = place(word_plane(ft.classes, CR_WORDS, CR_INFO, 2));
     for (size_t q = 0; q < 2; ++q) L.broad[q] = place(quad_plane(ft.broad, BR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.sel_words = uint32_t(ft.blob.size());   // the roundtrip kernel stages up to here
-    for (size_t q = 0; q < 4; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
+    for (size_t q = 0; q < XR_WORDS / 4; ++q) L.ext[q] = place(quad_plane(ft.ext, XR_WORDS, q));
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.hot_words = uint32_t(ft.blob.size());
     L.classes[3] = place(quad_plane(ft.classes, CR_WORDS, 3));   // read only when rank keys are compared: not staged

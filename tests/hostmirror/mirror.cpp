@@ -79,18 +79,11 @@ void mir_leaf_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* n_class
         if (ref) {
             while (!(ref & REF_LEAF)) {
                 ++steps;
-                uint32_t child;
-                if (ref & REF_BIT) {
-                    const uint32_t bit = (ref >> 20) & 127u, w = bit >> 5;
-                    const uint32_t limb = w == 0 ? c0 : (w == 1 ? c1 : c2);
-                    child = ref_index(ref) + ((limb >> (bit & 31u)) & 1u);
-                } else {
-                    const uint32_t* na = t.cold + t.at.nodes[0] + ref_index(ref) * 4;
-                    const uint32_t* nb = t.cold + t.at.nodes[1] + ref_index(ref) * 4;
-                    const uint32_t f = (c0 & na[0]) * na[3] + (c1 & na[1]) * nb[0] + (c2 & na[2]) * nb[3];
-                    child = nb[1] + (f >> nb[2]);
-                }
-                ref = t.cold[t.at.children + child];
+                const uint32_t* na = t.cold + t.at.nodes[0] + ref_index(ref) * 4;
+                const uint32_t* nb = t.cold + t.at.nodes[1] + ref_index(ref) * 4;
+                uint32_t f = (c2 & na[0]) * na[1];
+                if (ref & REF_WIDE) f += (c0 & nb[0]) * nb[2] + (c1 & nb[1]) * nb[3];
+                ref = t.cold[t.at.children + na[2] + (f >> na[3])];
             }
             start = ref_index(ref); count = ref_count(ref);
         }
