@@ -83,11 +83,12 @@ __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int
         atomicAdd(&counters[threadIdx.x], (unsigned long long)s_acc[threadIdx.x]);
 }
 
+// WIDE: the table has leaves of more than 16 classes (the SM120 table has none; its kernels leave that path out).
 // IDX is the type of the word index: uint32_t when the batch allows it (then every plane
 // address is one 32 x 32 + 64 bit multiply-add from a plane base that is the same for the
 // whole grid), uint64_t otherwise.  The next word of a thread is loaded before the current one
 // is decoded, so its latency hides behind the table walk.
-template <class HOT, class IDX>
+template <class HOT, class IDX, bool WIDE>
 __global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n64, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
@@ -104,7 +105,7 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n64, uint16
         uint4 next = w;
         if (n - i > step) next = __ldcs(words + (i + step));
         uint32_t f, c, s[8];
-        decode_word<HOT>(t, w.x, w.y, w.z, w.w, &f, s, &c);
+        decode_word<HOT, WIDE>(t, w.x, w.y, w.z, w.w, &f, s, &c);
         __stcs(form + i, (uint16_t)f);
 #pragma unroll
         for (int k = 0; k < 8; ++k) __stcs(slots + (uint64_t)k * slot_stride + i, s[k]);
@@ -186,7 +187,7 @@ encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __
     }
 }
 
-template <class HOT>
+template <class HOT, bool WIDE>
 __global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
@@ -195,11 +196,16 @@ roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8
     uint32_t n_exact = 0, n_rejected = 0;
     const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
     const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // The next word of a thread is loaded before the current one is checked.
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (first < n) w = __ldcs(words + first);
     for (uint64_t i = first; i < n; i += step) {
-        const uint4 w = __ldcs(words + i);
-        const uint32_t st = roundtrip_word<HOT>(t, w.x, w.y, w.z, w.w);
+        uint4 next = w;
+        if (n - i > step) next = __ldcs(words + (i + step));
+        const uint32_t st = roundtrip_word<HOT, WIDE>(t, w.x, w.y, w.z, w.w);
         __stcs(status + i, (uint8_t)st);
         n_exact += st == RT_EXACT; n_rejected += st == RT_REJECTED;
+        w = next;
     }
     if (counters) {
         const uint32_t seen = first < n ? (uint32_t)((n - first + step - 1) / step) : 0u;
@@ -294,6 +300,7 @@ thread_local std::string g_create_error;
 struct DeviceState {
     int device = -1;
     int sm_count = 0;
+    bool wide_leaves = false; // the table has a leaf of more than 16 classes: kernels with the wide-leaf path
     bool wide_index = false;  // CUBIT_WIDE_INDEX=1: 64-bit word indices at every batch size (otherwise only above 2^31 words)
     bool shared_ok = false;   // the hot part of the table fits the opt-in shared memory of this device
     bool rt_shared_ok = false;   // so do the roundtrip kernel's two ranges (selection tables + roundtrip constants)
@@ -442,6 +449,7 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     if (rc) return rc;
     d->view.cold = blob; d->view.at = ft.at;
     d->hot_bytes = ft.at.hot_words * 4;
+    d->wide_leaves = ft.max_leaf_classes > 16;
     {
         const char* wide = getenv("CUBIT_WIDE_INDEX");
         d->wide_index = wide && wide[0] == '1';
@@ -451,16 +459,22 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     CU_TRY(c, cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
     if (d->shared_ok) {
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        const int hot = (int)d->hot_bytes;
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
         CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotSharedEnc>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->hot_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
     }
     d->rt_bytes = (ft.at.sel_words + (ft.at.total_words - ft.at.rt[0])) * 4;
     d->rt_shared_ok = d->shared_ok && (int)d->rt_bytes + 1024 <= optin;
-    if (d->rt_shared_ok)
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+    if (d->rt_shared_ok) {
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+    }
     CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
     for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
     CU_TRY(c, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
@@ -483,19 +497,22 @@ int grid_shared(const DeviceState* d, uint64_t n) {
 
 void launch_decode(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint16_t* form, uint32_t* slots,
                    uint64_t stride, uint32_t* ctrl, unsigned long long* dc) {
-    // 32-bit word indices while index + grid size cannot wrap.
+    // 32-bit word indices while index + grid size cannot wrap; kernels without the wide-leaf path when the
+    // table has no such leaf.
     const bool narrow = n < (1ull << 31) && !d->wide_index;
-    if (use_shared(d, n)) {
-        if (narrow)
-            decode_kernel<HotShared, uint32_t><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
-        else
-            decode_kernel<HotShared, uint64_t><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+    const bool staged = use_shared(d, n);
+    const int grid = staged ? grid_shared(d, n) : grid_for(d, n), block = staged ? kBlockShared : kBlock;
+    const size_t smem = staged ? d->hot_bytes : 0;
+#define CB_LAUNCH_DECODE(HOT, IDX, WIDE) \
+    decode_kernel<HOT, IDX, WIDE><<<grid, block, smem, s>>>(d->view, words, n, form, slots, stride, ctrl, dc)
+    if (staged) {
+        if (d->wide_leaves) { if (narrow) CB_LAUNCH_DECODE(HotShared, uint32_t, true); else CB_LAUNCH_DECODE(HotShared, uint64_t, true); }
+        else { if (narrow) CB_LAUNCH_DECODE(HotShared, uint32_t, false); else CB_LAUNCH_DECODE(HotShared, uint64_t, false); }
     } else {
-        if (narrow)
-            decode_kernel<HotGlobal, uint32_t><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
-        else
-            decode_kernel<HotGlobal, uint64_t><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);
+        if (d->wide_leaves) { if (narrow) CB_LAUNCH_DECODE(HotGlobal, uint32_t, true); else CB_LAUNCH_DECODE(HotGlobal, uint64_t, true); }
+        else { if (narrow) CB_LAUNCH_DECODE(HotGlobal, uint32_t, false); else CB_LAUNCH_DECODE(HotGlobal, uint64_t, false); }
     }
+#undef CB_LAUNCH_DECODE
 }
 void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, const uint32_t* slots, uint64_t stride,
                    const uint32_t* ctrl, uint64_t n, uint4* words) {
@@ -509,12 +526,15 @@ void launch_encode(const DeviceState* d, cudaStream_t s, const uint16_t* form, c
 }
 void launch_roundtrip(const DeviceState* d, cudaStream_t s, const uint4* words, uint64_t n, uint8_t* status,
                       unsigned long long* dc) {
-    if (use_shared(d, n) && d->rt_shared_ok)
-        roundtrip_kernel<HotSharedRT><<<grid_shared(d, n), kBlockShared, d->rt_bytes, s>>>(d->view, words, n, status, dc);
-    else if (use_shared(d, n))
-        roundtrip_kernel<HotShared><<<grid_shared(d, n), kBlockShared, d->hot_bytes, s>>>(d->view, words, n, status, dc);
-    else
-        roundtrip_kernel<HotGlobal><<<grid_for(d, n), kBlock, 0, s>>>(d->view, words, n, status, dc);
+#define CB_LAUNCH_RT(HOT, grid, block, smem)                                                          \
+    do {                                                                                              \
+        if (d->wide_leaves) roundtrip_kernel<HOT, true><<<grid, block, smem, s>>>(d->view, words, n, status, dc); \
+        else roundtrip_kernel<HOT, false><<<grid, block, smem, s>>>(d->view, words, n, status, dc);   \
+    } while (0)
+    if (use_shared(d, n) && d->rt_shared_ok) CB_LAUNCH_RT(HotSharedRT, grid_shared(d, n), kBlockShared, d->rt_bytes);
+    else if (use_shared(d, n)) CB_LAUNCH_RT(HotShared, grid_shared(d, n), kBlockShared, d->hot_bytes);
+    else CB_LAUNCH_RT(HotGlobal, grid_for(d, n), kBlock, 0);
+#undef CB_LAUNCH_RT
 }
 
 DeviceState* device_of_pointer(cubit_ctx* ctx, const void* p) {
