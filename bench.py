@@ -135,12 +135,11 @@ def run_cubin(args, rank, world, local):
 DEFAULT_WORDS = 64 * 1024 * 1024    # 1 GiB of 16-byte words
 STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per word of one captured launch, from the ncu summaries
-# under profiles/ (smaller cases than the bench's, scaled by the word count: the traffic is the
-# stream itself, read and written once).  decode: (268.7 MB + 580.7 MB) / 16 Mi words;
-# encode: (319.0 MB + 99.8 MB) / 8 Mi; roundtrip: (134.5 MB + 6.2 MB) / 8 Mi.  Part of the last
-# writes of a captured launch is still in L2 when it ends, more so in the smaller captures.
-NCU_DRAM_BYTES_PER_WORD = {"decode": 50.6, "encode": 49.9, "roundtrip": 16.8}
+# dram__bytes_read.sum + dram__bytes_write.sum per word of one captured launch, from the newest ncu summaries
+# under profiles/ (8 Mi-word captures, scaled by the word count: the traffic is the stream itself, read
+# and written once).  decode: (134.46 MB + 261.06 MB) / 8 Mi words; encode: (319.2 MB + 98.1 MB) / 8 Mi;
+# roundtrip: (134.47 MB + 6.11 MB) / 8 Mi.  Part of the last writes of a captured launch is still in L2 when it ends.
+NCU_DRAM_BYTES_PER_WORD = {"decode": 47.15, "encode": 49.74, "roundtrip": 16.76}
 # The capture each figure comes from (summaries under profiles/).
 NCU_CAPTURE = {"decode": "profiles/decode_kernel_zipf.md", "encode": "profiles/encode_kernel_records.md",
                "roundtrip": "profiles/roundtrip_kernel_mix.md"}
