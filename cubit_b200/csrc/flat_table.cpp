@@ -539,7 +539,7 @@ struct TreeBuilder {
                 const size_t cz = class_count(zero), co = class_count(one);
                 const size_t mx = std::max(cz, co), sum = cz + co;
                 // Candidates that do not check the bit are copied to both sides: bound that growth.
-                if (2 * sum > 3 * n_classes && !oversize) continue;
+                if (sum > 2 * n_classes && !oversize) continue;
                 if (mx < best_max || (mx == best_max && best_bit >= 0 && sum < best_sum)) {
                     best_max = mx; best_sum = sum; best_bit = bit; best_zero = zero; best_one = one;
                 }
