@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from . import build as _build
@@ -94,7 +95,8 @@ def load_library() -> C.CDLL:
     library every codec call fails."""
     global _lib
     if _lib is None:
-        path = _build.build()
+        # CUBIT_B200_LIB names a library file to load instead of the in-tree build (for comparing builds).
+        path = os.environ.get("CUBIT_B200_LIB") or _build.build()
         lib = C.CDLL(str(path))
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)   # AttributeError here means the library lacks a declared symbol

@@ -899,6 +899,16 @@ FlatTable FlatTable::compile(const IsaTable& t) {
             ext_of[vi] = it->second;
             ft.var[vi * VR_WORDS + VR_EXT] = it->second;
         }
+        // The all-zero record (no field, no flag, no synthesized modifier): what a rejected word is extracted through.
+        {
+            const std::vector<uint32_t> zero(XR_WORDS, 0);
+            auto it = seen.find(zero);
+            if (it == seen.end()) {
+                it = seen.emplace(zero, uint32_t(unique.size() / XR_WORDS)).first;
+                unique.insert(unique.end(), zero.begin(), zero.end());
+            }
+            ft.at.zero_ext = it->second;
+        }
         if (unique.size() / XR_WORDS > 0xFFFF) throw std::runtime_error("too many distinct field layouts");
         ft.ext.swap(unique);
     }
