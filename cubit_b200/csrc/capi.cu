@@ -84,12 +84,13 @@ __device__ __forceinline__ void block_tally(const uint32_t (&mine)[N], const int
 }
 
 // WIDE: the table has leaves of more than 16 classes (the SM120 table has none; its kernels leave that path out).
+// COUNT: the caller wants the counters (launches without them leave the per-word tallies out).
 // IDX is the type of the word index: uint32_t when the batch allows it (then every plane
 // address is one 32 x 32 + 64 bit multiply-add from a plane base that is the same for the
 // whole grid), uint64_t otherwise.  The next word of a thread is loaded before the current one
 // is decoded, so its latency hides behind the table walk.
-template <class HOT, class IDX, bool WIDE>
-__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
+template <class HOT, class IDX, bool WIDE, bool COUNT>
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared, 1)
 decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n64, uint16_t* __restrict__ form,
               uint32_t* __restrict__ slots, uint64_t slot_stride, uint32_t* __restrict__ ctrl,
               unsigned long long* counters) {
@@ -110,11 +111,13 @@ decode_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n64, uint16
 #pragma unroll
         for (int k = 0; k < 8; ++k) __stcs(slots + (uint64_t)k * slot_stride + i, s[k]);
         __stcs(ctrl + i, c);
-        n_ok += (c >> 30) == ST_OK;
-        n_tie += (c >> 28) & 1u;
+        if (COUNT) {
+            n_ok += (c >> 30) == ST_OK;
+            n_tie += (c >> 28) & 1u;
+        }
         w = next;
     }
-    if (counters) {
+    if (COUNT) {
         // Rejected words are the rest of this thread's share of the batch.
         const uint32_t seen = first < n ? (uint32_t)((n - first + step - 1) / step) : 0u;
         const uint32_t tally[3] = {n_ok, seen - n_ok, n_tie};
@@ -188,7 +191,7 @@ encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __
 }
 
 template <class HOT, bool WIDE>
-__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared)
+__global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared, 1)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
     stage_table<HOT>(tg, 0, tg.at.hot_words);
@@ -460,10 +463,13 @@ int init_device(const FlatTable& ft, DeviceState* d) {
     d->shared_ok = (int)d->hot_bytes + 1024 <= optin && (int)d->enc_bytes + 1024 <= optin;
     if (d->shared_ok) {
         const int hot = (int)d->hot_bytes;
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
-        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, uint64_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+#define CB_DECODE_SMEM(IDX, WIDE, COUNT) \
+        CU_TRY(c, cudaFuncSetAttribute(decode_kernel<HotShared, IDX, WIDE, COUNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot))
+        CB_DECODE_SMEM(uint32_t, true, true); CB_DECODE_SMEM(uint32_t, true, false);
+        CB_DECODE_SMEM(uint64_t, true, true); CB_DECODE_SMEM(uint64_t, true, false);
+        CB_DECODE_SMEM(uint32_t, false, true); CB_DECODE_SMEM(uint32_t, false, false);
+        CB_DECODE_SMEM(uint64_t, false, true); CB_DECODE_SMEM(uint64_t, false, false);
+#undef CB_DECODE_SMEM
         CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotSharedEnc>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
         CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
@@ -503,8 +509,11 @@ void launch_decode(const DeviceState* d, cudaStream_t s, const uint4* words, uin
     const bool staged = use_shared(d, n);
     const int grid = staged ? grid_shared(d, n) : grid_for(d, n), block = staged ? kBlockShared : kBlock;
     const size_t smem = staged ? d->hot_bytes : 0;
-#define CB_LAUNCH_DECODE(HOT, IDX, WIDE) \
-    decode_kernel<HOT, IDX, WIDE><<<grid, block, smem, s>>>(d->view, words, n, form, slots, stride, ctrl, dc)
+#define CB_LAUNCH_DECODE(HOT, IDX, WIDE)                                                                             \
+    do {                                                                                                             \
+        if (dc) decode_kernel<HOT, IDX, WIDE, true><<<grid, block, smem, s>>>(d->view, words, n, form, slots, stride, ctrl, dc); \
+        else decode_kernel<HOT, IDX, WIDE, false><<<grid, block, smem, s>>>(d->view, words, n, form, slots, stride, ctrl, dc);  \
+    } while (0)
     if (staged) {
         if (d->wide_leaves) { if (narrow) CB_LAUNCH_DECODE(HotShared, uint32_t, true); else CB_LAUNCH_DECODE(HotShared, uint64_t, true); }
         else { if (narrow) CB_LAUNCH_DECODE(HotShared, uint32_t, false); else CB_LAUNCH_DECODE(HotShared, uint64_t, false); }
