@@ -190,7 +190,7 @@ encode_kernel(FlatView tg, const uint16_t* __restrict__ form, const uint32_t* __
     }
 }
 
-template <class HOT, bool WIDE>
+template <class HOT, bool WIDE, bool COUNT>
 __global__ void __launch_bounds__(std::is_same<HOT, HotGlobal>::value ? kBlock : kBlockShared, 1)
 roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8_t* __restrict__ status,
                  unsigned long long* counters) {
@@ -207,10 +207,10 @@ roundtrip_kernel(FlatView tg, const uint4* __restrict__ words, uint64_t n, uint8
         if (n - i > step) next = __ldcs(words + (i + step));
         const uint32_t st = roundtrip_word<HOT, WIDE>(t, w.x, w.y, w.z, w.w);
         __stcs(status + i, (uint8_t)st);
-        n_exact += st == RT_EXACT; n_rejected += st == RT_REJECTED;
+        if (COUNT) { n_exact += st == RT_EXACT; n_rejected += st == RT_REJECTED; }
         w = next;
     }
-    if (counters) {
+    if (COUNT) {
         const uint32_t seen = first < n ? (uint32_t)((n - first + step - 1) / step) : 0u;
         const uint32_t tally[3] = {n_exact, seen - n_exact - n_rejected, n_rejected};
         const int which[3] = {CNT_EXACT, CNT_MISMATCH, CNT_REJECTED};
@@ -471,15 +471,19 @@ int init_device(const FlatTable& ft, DeviceState* d) {
         CB_DECODE_SMEM(uint64_t, false, true); CB_DECODE_SMEM(uint64_t, false, false);
 #undef CB_DECODE_SMEM
         CU_TRY(c, cudaFuncSetAttribute(encode_kernel<HotSharedEnc>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->enc_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotShared, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
         CU_TRY(c, cudaFuncSetAttribute(meta_kernel<HotShared>, cudaFuncAttributeMaxDynamicSharedMemorySize, hot));
     }
     d->rt_bytes = (ft.at.sel_words + (ft.at.total_words - ft.at.rt[0])) * 4;
     d->rt_shared_ok = d->shared_ok && (int)d->rt_bytes + 1024 <= optin;
     if (d->rt_shared_ok) {
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
-        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
+        CU_TRY(c, cudaFuncSetAttribute(roundtrip_kernel<HotSharedRT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d->rt_bytes));
     }
     CU_TRY(c, cudaMalloc((void**)&d->counters, sizeof(unsigned long long) * CNT_WORDS * kCounterSlots));
     for (int s = 0; s < kCounterSlots; ++s) d->free_counter_slots.push_back(s);
@@ -537,8 +541,13 @@ void launch_roundtrip(const DeviceState* d, cudaStream_t s, const uint4* words, 
                       unsigned long long* dc) {
 #define CB_LAUNCH_RT(HOT, grid, block, smem)                                                          \
     do {                                                                                              \
-        if (d->wide_leaves) roundtrip_kernel<HOT, true><<<grid, block, smem, s>>>(d->view, words, n, status, dc); \
-        else roundtrip_kernel<HOT, false><<<grid, block, smem, s>>>(d->view, words, n, status, dc);   \
+        if (d->wide_leaves) {                                                                         \
+            if (dc) roundtrip_kernel<HOT, true, true><<<grid, block, smem, s>>>(d->view, words, n, status, dc);   \
+            else roundtrip_kernel<HOT, true, false><<<grid, block, smem, s>>>(d->view, words, n, status, dc);     \
+        } else {                                                                                      \
+            if (dc) roundtrip_kernel<HOT, false, true><<<grid, block, smem, s>>>(d->view, words, n, status, dc);  \
+            else roundtrip_kernel<HOT, false, false><<<grid, block, smem, s>>>(d->view, words, n, status, dc);    \
+        }                                                                                             \
     } while (0)
     if (use_shared(d, n) && d->rt_shared_ok) CB_LAUNCH_RT(HotSharedRT, grid_shared(d, n), kBlockShared, d->rt_bytes);
     else if (use_shared(d, n)) CB_LAUNCH_RT(HotShared, grid_shared(d, n), kBlockShared, d->hot_bytes);
