@@ -192,6 +192,25 @@ struct TreeBuilder {
             key_of[vs[i]] = (uint32_t(s.score < 0 ? 1 : 0) << 31) | (mid_rank[s.mid] << 22) | (lo_rank[s.lo] << 8) | uint32_t(i);
         }
 
+        // Choice flags that no rule can ask for inside this leaf are dropped from its records, so that they
+        // do not show up as "carried by some candidate but not by the top one" and send the kernel into
+        // the rule choice for nothing: the LEA flags without a LEA form among the candidates, the _UP flag
+        // without a uniform LOP3 form, the branch-mode flags without a BRA form, and "no middle predicate"
+        // when every candidate has it (the rule asks for it only when the top candidate lacks it).
+        uint32_t strip = 0;
+        {
+            bool lea = false, ulop3 = false, bra = false, all_no_mid = true;
+            for (uint32_t v : vs) {
+                const uint32_t f = st[v].flags;
+                lea |= (f & FL1_IS_LEA) != 0; ulop3 |= (f & FL1_IS_ULOP3) != 0; bra |= (f & FL_IS_BRA) != 0;
+                all_no_mid &= (f & FL_NO_MID_P) != 0;
+            }
+            if (!lea) strip |= FL_LEA_A1 | FL_LEA_A2;
+            if (!ulop3) strip |= FL_ENDS_UP;
+            if (!bra) strip |= FL_EXP_U | FL_EXP_DIV | FL_EXP_CONV | FL_GRP_U | FL_GRP_DIV | FL_GRP_CONV | FL_BRA_NOMODE;
+            if (all_no_mid) strip |= FL_NO_MID_P;
+        }
+        auto flags_of = [&](uint32_t v) { return st[v].flags & ~strip; };
         std::map<ClassKey, std::vector<uint32_t>> groups;
         std::vector<ClassKey> order;   // classes in order of their first (canonical) member
         for (uint32_t v : vs) {
@@ -269,20 +288,23 @@ struct TreeBuilder {
             rec[CR_GROUP] = group_mask;
             // Leaves of at most 16 classes keep the best member's output-predicate field mask above the group bits.
             if (order.size() <= 16) rec[CR_GROUP] |= r2_mask_of(best.flags) & 0xFFFF0000u;
-            rec[CR_FIRST_FLAGS] = best.flags;
+            rec[CR_FIRST_FLAGS] = flags_of(mem[0]);
             rec[CR_KEY] = key_of[mem[0]] | (tie_within ? (uint32_t)KEY_WITHIN : 0u);
             rec[CR_BEST] = mem[0] | (ext_of[mem[0]] << 16);
             uint32_t any = 0;
-            for (uint32_t v : mem) any |= st[v].flags & 0xFFFFu;
+            for (uint32_t v : mem) any |= flags_of(v) & 0xFFFFu;
             if (mem.size() > 1) {
                 // Best member per choice flag (members are in rank order) and whether it is tied.
+                // The per-flag tables are indexed by the class itself (classes with one member leave a gap),
+                // so the kernel finds one without reading the class's cold quad first.
+                ft.flagbest.resize((size_t(first_class) + ci) * FB_WORDS, 0);
                 rec[CR_FLAGBEST] = uint32_t(ft.flagbest.size() / FB_WORDS);
                 uint32_t fb[FB_WORDS] = {0};
                 for (int f = 0; f < 16; ++f) {
                     int seen = 0;
                     uint32_t first_key = 0;
                     for (uint32_t v : mem) {
-                        if (!((st[v].flags >> f) & 1u)) continue;
+                        if (!((flags_of(v) >> f) & 1u)) continue;
                         if (seen == 0) { first_key = key_of[v]; fb[2 * f] = key_of[v]; fb[2 * f + 1] = v | (ext_of[v] << 16); }
                         else if (seen == 1 && (key_of[v] >> KEY_TUPLE_SHIFT) == (first_key >> KEY_TUPLE_SHIFT)) fb[2 * f] |= KEY_WITHIN;
                         ++seen;

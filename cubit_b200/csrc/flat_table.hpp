@@ -36,7 +36,7 @@ struct FlatTable {
     std::vector<uint32_t> nodes;     // NR_WORDS each
     std::vector<uint32_t> children;  // refs
     std::vector<uint32_t> classes;   // CR_WORDS each
-    std::vector<uint32_t> flagbest;  // FB_WORDS per class that has several members
+    std::vector<uint32_t> flagbest;  // FB_WORDS per class, indexed by the class; filled for classes that have several members
     std::vector<uint8_t> memo;       // MEMO_BYTES per memo leaf
     std::vector<uint32_t> broad;     // BR_WORDS each
     std::vector<uint32_t> ext;       // XR_WORDS per distinct field layout
