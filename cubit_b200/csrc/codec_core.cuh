@@ -153,14 +153,6 @@ enum { KEY_PRIO_POS = 29, KEY_POPC_POS = 15, KEY_TUPLE_SHIFT = 8 };
 // stored key says that the class's best member shares its rank tuple with another member.
 enum : uint32_t { KEY_WITHIN = 1u << 29 };
 
-// Ranking memo.  Inside a leaf of at most MEMO_MAX_CLASSES classes whose word-dependent rank
-// part reads nothing but the guard nibble (and_base bits outside the strict mask all lie in
-// bits 15:12), the top-ranked candidate is a function of (guard nibble, set of strictly
-// matching classes).  The table compiler evaluates the ranking loop for every such pair and
-// stores winner and tie flag in one byte; in those leaves CR_GROUP carries the leaf's memo
-// number + 1 above its low MEMO_MAX_CLASSES bits.
-enum : uint32_t { MEMO_MAX_CLASSES = 6, MEMO_BYTES = 16u << MEMO_MAX_CLASSES, MEMO_TIE = 0x80u, MEMO_WINNER_MASK = 0x1Fu };
-
 // Extraction record, 12 u32 (three quads), hot; variants with the same field layout share one.
 // Layout 0 gives every multi-bit field a slot of its own by the limb it lies in (no stored
 // field crosses a 32-bit limb there): slots 0..2 read limb 0, slot 3 limb 1, slot 4 limb 2,
@@ -239,7 +231,6 @@ struct BlobLayout {
     uint32_t enc_end;     // encode window: [enc, enc_end) holds the deposit and variant records
     uint32_t flagbest, gfields, metaf;
     uint32_t gindex;      // per variant: first generator field | field count << 24 (into gfields)
-    uint32_t memo;        // ranking memo: MEMO_BYTES per memo leaf, one byte per (guard nibble, strict-match mask)
     uint32_t rt[2];       // roundtrip constants: per variant {A0, A1, A2, E3 | mask index << 9}; per distinct mask
                           // {~M0, ~M1, ~M2, reuse keep | const << 3}.  The two planes are adjacent and end the blob
                           // (at total_words).
@@ -633,7 +624,7 @@ CB_HD void fold_flagged(const FlatView& t, uint32_t ci, uint32_t prio, uint32_t 
 // function would copy it to the stack.)
 struct WideLeafArgs {
     const uint32_t* cold;
-    uint32_t classes[4], class_info, broad[2], flagbest, memo;
+    uint32_t classes[4], class_info, broad[2], flagbest;
 };
 template <class HOT>
 CB_HD_COLD uint32_t select_in_wide_leaf(WideLeafArgs wa, uint32_t start, uint32_t count, uint32_t c0, uint32_t c1, uint32_t c2,
@@ -643,7 +634,7 @@ CB_HD_COLD uint32_t select_in_wide_leaf(WideLeafArgs wa, uint32_t start, uint32_
     for (int k = 0; k < 4; ++k) t.at.classes[k] = wa.classes[k];
     t.at.class_info = wa.class_info;
     t.at.broad[0] = wa.broad[0]; t.at.broad[1] = wa.broad[1];
-    t.at.flagbest = wa.flagbest; t.at.memo = wa.memo;
+    t.at.flagbest = wa.flagbest;
     *best = FORM_NONE;
     *tie = 0;
 
@@ -692,19 +683,10 @@ CB_HD_COLD uint32_t select_in_wide_leaf(WideLeafArgs wa, uint32_t start, uint32_
             const uint32_t f = cb_lowest_bit(strict);
             const Quad q2f = HOT::q(t, t.at.classes[2] + (r0 + f) * 4u);
             if (broad == 0 || !(q2f.x >> 31)) {
-                const bool small = count <= MEMO_MAX_CLASSES;
-                const uint32_t memo = small ? (q2f.w >> MEMO_MAX_CLASSES) : 0u;
-                mm = q2f.w & strict;   // in a small leaf strict has no bit where the memo id sits
+                mm = q2f.w & strict;
                 if (mm == (1u << f)) {
                     first_key = q2f.x; first_fl = q2f.y; first_best = q2f.z;
                     tie_first = (q2f.x & KEY_WITHIN) ? 1u : 0u;
-                    mm = 0;
-                } else if (memo) {
-                    const uint32_t at = (memo - 1u) * MEMO_BYTES + ((((c0 >> 12) & 15u) << MEMO_MAX_CLASSES) | strict);
-                    const uint32_t e = (cb_ld(t.cold + t.at.memo + (at >> 2)) >> (8u * (at & 3u))) & 0xFFu;
-                    const Quad q2 = HOT::q(t, t.at.classes[2] + (r0 + (e & MEMO_WINNER_MASK)) * 4u);
-                    first_key = q2.x; first_fl = q2.y; first_best = q2.z;
-                    tie_first = (e & MEMO_TIE) ? 1u : 0u;
                     mm = 0;
                 }
             }
@@ -765,7 +747,7 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         for (int k = 0; k < 4; ++k) wa.classes[k] = t.at.classes[k];
         wa.class_info = t.at.class_info;
         wa.broad[0] = t.at.broad[0]; wa.broad[1] = t.at.broad[1];
-        wa.flagbest = t.at.flagbest; wa.memo = t.at.memo;
+        wa.flagbest = t.at.flagbest;
         uint32_t wide_best, wide_tie;
         const uint32_t st = select_in_wide_leaf<HOT>(wa, start, count, c0, c1, c2, &wide_best, &wide_tie);
         *best = wide_best; *tie = wide_tie;
@@ -825,19 +807,10 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         const uint32_t f = cb_lowest_bit(strict);
         const Quad q2f = HOT::q(t, at2 + f * 4u);
         if (broad == 0 || !(q2f.x >> 31)) {
-            const bool small = count <= MEMO_MAX_CLASSES;
-            const uint32_t memo = small ? ((q2f.w & 0xFFFFu) >> MEMO_MAX_CLASSES) : 0u;
-            mm = q2f.w & strict;   // strict has no bit where the memo number or the field mask sits
+            mm = q2f.w & strict;   // strict has no bit where the field mask sits
             if (mm == (1u << f)) {
                 first_key = q2f.x; first_fl = q2f.y; first_best = q2f.z; first_r2 = q2f.w;
                 tie_first = (q2f.x & KEY_WITHIN) ? 1u : 0u;
-                mm = 0;
-            } else if (memo) {
-                const uint32_t at = (memo - 1u) * MEMO_BYTES + ((((c0 >> 12) & 15u) << MEMO_MAX_CLASSES) | strict);
-                const uint32_t e = (cb_ld(t.cold + t.at.memo + (at >> 2)) >> (8u * (at & 3u))) & 0xFFu;
-                const Quad q2 = HOT::q(t, at2 + (e & MEMO_WINNER_MASK) * 4u);
-                first_key = q2.x; first_fl = q2.y; first_best = q2.z; first_r2 = q2.w;
-                tie_first = (e & MEMO_TIE) ? 1u : 0u;
                 mm = 0;
             }
         }

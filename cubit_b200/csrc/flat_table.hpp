@@ -37,7 +37,6 @@ struct FlatTable {
     std::vector<uint32_t> children;  // refs
     std::vector<uint32_t> classes;   // CR_WORDS each
     std::vector<uint32_t> flagbest;  // FB_WORDS per class, indexed by the class; filled for classes that have several members
-    std::vector<uint8_t> memo;       // MEMO_BYTES per memo leaf
     std::vector<uint32_t> broad;     // BR_WORDS each
     std::vector<uint32_t> ext;       // XR_WORDS per distinct field layout
     std::vector<uint32_t> enc;       // ER_WORDS per distinct field layout: the encoder's view of `ext`
@@ -52,7 +51,6 @@ struct FlatTable {
     uint32_t n_buckets = 0;
     uint32_t max_bucket = 0;         // variants sharing one value of the opcode bits
     uint32_t n_leaves = 0;
-    uint32_t n_memo_leaves = 0;      // leaves whose word-dependent ranking is precomputed
     uint32_t max_leaf_classes = 0;
     uint32_t max_depth = 0;
 

@@ -61,11 +61,11 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 31 u32).
+// The compiled table blob and its section offsets (BlobLayout as 30 u32).
 void mir_blob(void* h, const uint32_t** blob, uint32_t* layout_words) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 31 * sizeof(uint32_t), "layout size");
+    static_assert(sizeof(BlobLayout) == 30 * sizeof(uint32_t), "layout size");
     memcpy(layout_words, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
@@ -119,31 +119,6 @@ void mir_rule_stats(void* h, const uint32_t* words, uint64_t n, uint32_t* need_o
     }
 }
 // Per word: how many classes the ranking loop has to compare (0: decided by static order alone).
-void mir_rank_stats(void* h, const uint32_t* words, uint64_t n, uint8_t* loop_len) {
-    const Mirror* m = (const Mirror*)h;
-    const FlatView& t = m->view;
-    for (uint64_t i = 0; i < n; ++i) {
-        const uint32_t c0 = words[4 * i], c1 = words[4 * i + 1], c2 = words[4 * i + 2];
-        loop_len[i] = 0;
-        uint32_t start, count;
-        if (find_leaf<HotPlain>(t, c0, c1, c2, &start, &count) != ST_OK || count > 32) continue;
-        uint32_t strict = 0, broad = 0;
-        for (uint32_t k = 0; k < count; ++k) {
-            uint32_t fl;
-            const uint32_t prio = class_match<HotPlain>(t, start + k, c0, c1, c2, &fl);
-            strict |= (prio == 0) << k; broad |= (prio == 2) << k;
-        }
-        uint32_t mm = strict | broad;
-        if (strict && (broad == 0 || !(HotPlain::q(t, t.at.classes[2] + (start + cb_lowest_bit(strict)) * 4u).x >> 31))) {
-            const uint32_t f = cb_lowest_bit(strict);
-            const uint32_t gw = HotPlain::q(t, t.at.classes[3] + (start + f) * 4u).w;
-            const bool small = count <= MEMO_MAX_CLASSES;
-            mm = (small ? (gw & ((1u << MEMO_MAX_CLASSES) - 1u)) : gw) & strict;
-            if (mm == (1u << f) || (small && (gw >> MEMO_MAX_CLASSES))) mm = 0;
-        }
-        loop_len[i] = (uint8_t)__builtin_popcount(mm);
-    }
-}
 void mir_word_meta(void* h, const uint32_t* words, uint64_t n, uint32_t* max_reg, uint32_t* barriers, uint8_t* is_exit) {
     const Mirror* m = (const Mirror*)h;
     for (uint64_t i = 0; i < n; ++i) {
