@@ -109,8 +109,11 @@ enum : uint32_t {           // CR_INFO
     CI_BROAD_MASK = 0xFFFu,
     CI_HAS_BROAD = 1u << 12,
     CI_SEVERAL = 1u << 13,        // the class has more than one member
-    CI_RELEVANT_POS = 16,         // 16 bits, the same in every class of a leaf: which of the leaf's first sixteen classes
-                                  // have a broad record that still matters when some class matched strictly
+    CI_LEAF_POS = 16,             // the upper halves hold words of the whole leaf (one bit per class, leaves of at most 16):
+                                  // in the leaf's first class CR_INFO the classes with a broad record that still matters
+                                  // when some class matched strictly and CR_ANY_FLAGS all classes with a broad record,
+                                  // in its second class CR_INFO the classes whose strict match, as the first of the
+                                  // leaf, settles the outcome
 };
 enum { BR_WORDS = 8 };      // broad record (hot): mask[3], base[3], pad
 // Per-flag table (cold) of a class with several members: for each of the 16 choice flags the
@@ -770,6 +773,9 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         typename HOT::Cursor p0 = HOT::at(t, t.at.classes[0] + start * 4u), p1 = HOT::at(t, t.at.classes[1] + start * 2u);
         uint32_t bit = 1u;
         const uint32_t end = 1u << count;
+        // Which classes settle the outcome when they are the first to match (a word of the whole leaf, kept with
+        // its second class; a leaf of one class reads its neighbour's, which cannot end its loop any earlier).
+        const uint32_t settles = HOT::w(t, t.at.class_info + start * 2u + 2u) >> CI_LEAF_POS;
 #pragma unroll 1
         do {
             const Quad a = HOT::q_at(p0);
@@ -779,7 +785,9 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
             strict |= hit ? bit : 0u;
             any |= hit ? a.x : 0u;
             bit <<= 1;
-        } while (bit != end);
+            // A first match that settles the outcome ends the lane's walk over the leaf: all of strict lies inside
+            // `settles` exactly when its only bit is such a class (a first match outside it stays in strict for good).
+        } while (bit != end && !((strict - 1u) < (strict & settles)));
     }
     uint32_t broad = 0;
     if ((leaf_ref & REF_BROAD) && (!strict || (leaf_ref & REF_BROAD_ALWAYS))) {

@@ -4,6 +4,8 @@
 #include <array>
 #include <cmath>
 #include <cstring>
+#include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <stdexcept>
 #include <tuple>
@@ -402,10 +404,28 @@ struct TreeBuilder {
                 if ((rec[CR_INFO] & CI_HAS_BROAD) && (!nonneg || (rec[CR_ANY_FLAGS] & 0xFFFFu & ~common))) leaf_relevant |= 1u << ci;
             }
         }
-        for (size_t ci = 0; ci < order.size(); ++ci) {
-            uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
+        // Leaf-wide words ride in the upper halves of the first classes' info pair: the first class holds the
+        // broad records that still matter beside a strict match and all broad records, the second one the
+        // classes that settle the outcome.
+        // Such a class, when it is the first strict match of the leaf, decides everything: no later class can
+        // outrank or tie it, no member of it or of a later class carries a flag that a rule could ask for under
+        // it, and no broad record matters next to a strict match.  The kernel stops testing the leaf's classes
+        // there.
+        uint32_t settles = 0;
+        if (order.size() <= 16 && leaf_relevant == 0) {
+            uint32_t later_flags = 0;
+            for (size_t ci = order.size(); ci-- > 0;) {
+                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
+                const bool no_later_rival = (rec[CR_GROUP] & 0xFFFFu & ~((2u << ci) - 1u)) == 0;
+                later_flags |= rec[CR_ANY_FLAGS] & 0xFFFFu;
+                if (st[groups[order[ci]][0]].s_ok && no_later_rival && !(later_flags & ~rec[CR_FIRST_FLAGS])) settles |= 1u << ci;
+            }
+        }
+        {
+            uint32_t* rec = &ft.classes[size_t(first_class) * CR_WORDS];
             rec[CR_ANY_FLAGS] |= leaf_broad16 << 16;
-            rec[CR_INFO] |= leaf_relevant << CI_RELEVANT_POS;
+            rec[CR_INFO] |= leaf_relevant << CI_LEAF_POS;
+            if (order.size() > 1) rec[CR_WORDS + CR_INFO] |= settles << CI_LEAF_POS;
         }
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
