@@ -109,11 +109,11 @@ enum : uint32_t {           // CR_INFO
     CI_BROAD_MASK = 0xFFFu,
     CI_HAS_BROAD = 1u << 12,
     CI_SEVERAL = 1u << 13,        // the class has more than one member
-    CI_LEAF_POS = 16,             // the upper halves hold words of the whole leaf (one bit per class, leaves of at most 16):
-                                  // in the leaf's first class CR_INFO the classes with a broad record that still matters
-                                  // when some class matched strictly and CR_ANY_FLAGS all classes with a broad record,
-                                  // in its second class CR_INFO the classes whose strict match, as the first of the
-                                  // leaf, settles the outcome
+    CI_LEAF_POS = 16,             // the upper halves hold one bit per class of the leaf (leaves of at most 16 classes):
+                                  // CR_INFO: the classes with a broad record that still matters when this class is the
+                                  // first strict match; CR_ANY_FLAGS of the leaf's first class: all classes with a broad
+                                  // record; CR_ANY_FLAGS of its second class: the classes whose strict match, as the first
+                                  // of the leaf, settles the outcome
 };
 enum { BR_WORDS = 8 };      // broad record (hot): mask[3], base[3], pad
 // Per-flag table (cold) of a class with several members: for each of the 16 choice flags the
@@ -775,7 +775,7 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         const uint32_t end = 1u << count;
         // Which classes settle the outcome when they are the first to match (a word of the whole leaf, kept with
         // its second class; a leaf of one class reads its neighbour's, which cannot end its loop any earlier).
-        const uint32_t settles = HOT::w(t, t.at.class_info + start * 2u + 2u) >> CI_LEAF_POS;
+        const uint32_t settles = HOT::w(t, t.at.class_info + start * 2u + 3u) >> CI_LEAF_POS;
 #pragma unroll 1
         do {
             const Quad a = HOT::q_at(p0);
@@ -792,8 +792,10 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     uint32_t broad = 0;
     if ((leaf_ref & REF_BROAD) && (!strict || (leaf_ref & REF_BROAD_ALWAYS))) {
         const uint32_t ati = t.at.class_info + start * 2u;
-        const Pair leaf = HOT::d(t, ati);   // {relevant broad records << 16, all broad records << 16}
-        for (uint32_t pending = ((strict ? leaf.x : leaf.y) >> 16) & ~strict; pending; pending &= pending - 1u) {
+        // The broad records to test: all of the leaf's when nothing matched strictly, else the ones that still
+        // matter beside the first strict match.
+        const uint32_t which = strict ? HOT::w(t, ati + cb_lowest_bit(strict) * 2u) : HOT::w(t, ati + 1u);
+        for (uint32_t pending = (which >> CI_LEAF_POS) & ~strict; pending; pending &= pending - 1u) {
             const uint32_t i = cb_lowest_bit(pending);
             const Pair b = HOT::d(t, ati + i * 2u);
             const bool hit = class_broad<HOT>(t, b.x, c0, c1, c2);

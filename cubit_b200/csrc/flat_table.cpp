@@ -274,10 +274,17 @@ struct TreeBuilder {
         // (score sign, middle rank) and either different outside bits (word-dependent) or an
         // identical static tuple (a tie the ranking loop has to report).
         auto outside = [&](const ClassKey& c) { const Static& b = st[groups[c][0]]; return b.s_ok ? (b.base96 & ~b.smask) : ~(u128)0; };
+        // Two classes whose strict masks demand different values of some bit never match the same word strictly.
+        auto can_both_match = [&](const ClassKey& a, const ClassKey& b) {
+            const Static& x = st[groups[a][0]];
+            const Static& y = st[groups[b][0]];
+            return !x.s_ok || !y.s_ok || ((x.sbase ^ y.sbase) & x.smask & y.smask) == 0;
+        };
         auto unsettled = [&](const ClassKey& a, const ClassKey& b) {
             const auto ka = sort_key(a), kb = sort_key(b);
             if (std::get<0>(ka) != std::get<0>(kb)) return false;
             if (!st[groups[a][0]].s_ok || !st[groups[b][0]].s_ok) return true;
+            if (!can_both_match(a, b)) return false;   // never strict matches of the same word
             // x beats y on every word when the constant part of its popcount leads by more than y's and_base
             // bits outside the masks can make up for, or leads by exactly that much and its low rank is better
             // (an equal low rank is a tie the ranking loop has to report).
@@ -384,49 +391,58 @@ struct TreeBuilder {
             ft.classes.insert(ft.classes.end(), rec, rec + CR_WORDS);
             leaf_group[ci] = group_mask; leaf_key[ci] = rec[CR_KEY] & ~(uint32_t)KEY_WITHIN; leaf_within[ci] = tie_within ? 1u : 0u;
         }
-        // Broad records that cannot change the outcome once some class matches strictly: every
-        // strictly matchable class of the leaf has a non-negative score (so a strict match is on
-        // top whatever else matches), and the class's choice flags are carried by the best member
-        // of each of them (so its flags add nothing to the union the rules look at, and the
-        // second pass, which asks for a flag the top candidate lacks, would pass it over).
+        // Broad records that cannot change the outcome once class k is the first strict match of the leaf: k has
+        // a non-negative score (so a strict match is on top whatever else matches: k itself or a later class of
+        // its group), and the broad class's choice flags are carried, or ruled out, by each of those possible
+        // top candidates (so its flags add nothing to what the rules look at, and the second pass, which asks
+        // for a flag the top candidate lacks, would pass it over).  The rest are the ones that still matter:
+        // one word per class, kept in the upper half of its info word.
+        const size_t n16 = std::min<size_t>(order.size(), 16);
+        std::vector<uint32_t> relevant(order.size(), 0);
         uint32_t leaf_relevant = 0;
-        {
-            uint32_t common = 0xFFFFu;
-            bool nonneg = true;
+        for (size_t k = 0; k < n16; ++k) {
+            const uint32_t* rk = &ft.classes[(size_t(first_class) + k) * CR_WORDS];
+            if (!st[groups[order[k]][0]].s_ok) continue;
+            uint32_t common = rk[CR_FIRST_FLAGS] & 0xFFFFu;
+            bool nonneg = !(rk[CR_KEY] >> 31);
+            if (order.size() <= 16) {
+                for (size_t j = k + 1; j < n16; ++j)
+                    if ((rk[CR_GROUP] >> j) & 1u) common &= ft.classes[(size_t(first_class) + j) * CR_WORDS + CR_FIRST_FLAGS];
+            } else {
+                // Leaves beyond 16 classes are ranked 32 at a time by a path of its own: one answer for the whole leaf.
+                for (size_t j = 0; j < order.size(); ++j) {
+                    const uint32_t* rj = &ft.classes[(size_t(first_class) + j) * CR_WORDS];
+                    if (!st[groups[order[j]][0]].s_ok) continue;
+                    common &= rj[CR_FIRST_FLAGS];
+                    if (rj[CR_KEY] >> 31) nonneg = false;
+                }
+            }
+            for (size_t j = 0; j < n16; ++j) {
+                const uint32_t* rj = &ft.classes[(size_t(first_class) + j) * CR_WORDS];
+                if ((rj[CR_INFO] & CI_HAS_BROAD) && (!nonneg || (rj[CR_ANY_FLAGS] & 0xFFFFu & ~common))) relevant[k] |= 1u << j;
+            }
+            leaf_relevant |= relevant[k];
+        }
+        // A class that, as the first strict match of the leaf, decides everything: no later class can outrank
+        // or tie it, no member of it or of a later class carries a flag that a rule could ask for under it, and
+        // no broad record matters next to it.  The kernel stops testing the leaf's classes there.
+        uint32_t settles = 0;
+        if (order.size() <= 16) {
             for (size_t ci = 0; ci < order.size(); ++ci) {
                 const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
-                if (!st[groups[order[ci]][0]].s_ok) continue;
-                common &= rec[CR_FIRST_FLAGS];
-                if (rec[CR_KEY] >> 31) nonneg = false;
-            }
-            for (size_t ci = 0; ci < order.size() && ci < 16; ++ci) {
-                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
-                if ((rec[CR_INFO] & CI_HAS_BROAD) && (!nonneg || (rec[CR_ANY_FLAGS] & 0xFFFFu & ~common))) leaf_relevant |= 1u << ci;
-            }
-        }
-        // Leaf-wide words ride in the upper halves of the first classes' info pair: the first class holds the
-        // broad records that still matter beside a strict match and all broad records, the second one the
-        // classes that settle the outcome.
-        // Such a class, when it is the first strict match of the leaf, decides everything: no later class can
-        // outrank or tie it, no member of it or of a later class carries a flag that a rule could ask for under
-        // it, and no broad record matters next to a strict match.  The kernel stops testing the leaf's classes
-        // there.
-        uint32_t settles = 0;
-        if (order.size() <= 16 && leaf_relevant == 0) {
-            uint32_t later_flags = 0;
-            for (size_t ci = order.size(); ci-- > 0;) {
-                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
                 const bool no_later_rival = (rec[CR_GROUP] & 0xFFFFu & ~((2u << ci) - 1u)) == 0;
-                later_flags |= rec[CR_ANY_FLAGS] & 0xFFFFu;
-                if (st[groups[order[ci]][0]].s_ok && no_later_rival && !(later_flags & ~rec[CR_FIRST_FLAGS])) settles |= 1u << ci;
+                uint32_t later_flags = rec[CR_ANY_FLAGS] & 0xFFFFu;   // its own members count: a rule may ask for another of them
+                for (size_t cj = ci + 1; cj < order.size(); ++cj)
+                    if (can_both_match(order[ci], order[cj])) later_flags |= ft.classes[(size_t(first_class) + cj) * CR_WORDS + CR_ANY_FLAGS] & 0xFFFFu;
+                if (st[groups[order[ci]][0]].s_ok && relevant[ci] == 0 && no_later_rival && !(later_flags & ~rec[CR_FIRST_FLAGS]))
+                    settles |= 1u << ci;
             }
         }
-        {
-            uint32_t* rec = &ft.classes[size_t(first_class) * CR_WORDS];
-            rec[CR_ANY_FLAGS] |= leaf_broad16 << 16;
-            rec[CR_INFO] |= leaf_relevant << CI_LEAF_POS;
-            if (order.size() > 1) rec[CR_WORDS + CR_INFO] |= settles << CI_LEAF_POS;
-        }
+        // Words of the whole leaf ride in the upper halves of the first two classes' flag words.
+        for (size_t ci = 0; ci < n16; ++ci)
+            ft.classes[(size_t(first_class) + ci) * CR_WORDS + CR_INFO] |= relevant[ci] << CI_LEAF_POS;
+        ft.classes[size_t(first_class) * CR_WORDS + CR_ANY_FLAGS] |= leaf_broad16 << CI_LEAF_POS;
+        if (order.size() > 1) ft.classes[(size_t(first_class) + 1) * CR_WORDS + CR_ANY_FLAGS] |= settles << CI_LEAF_POS;
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
         return REF_LEAF | first_class | (uint32_t(order.size()) << 20) | (leaf_has_broad ? uint32_t(REF_BROAD) : 0u) |
