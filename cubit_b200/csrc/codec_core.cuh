@@ -89,7 +89,9 @@ enum {                      // hash node record, 8 u32 (two quads)
 // so mask[0] carries the OR of the members' choice flags there and base[0] has zeros.
 enum {
     CR_SMASK = 0,           // [0..2] strict match mask; [0] bits 15:0: OR of the members' choice flags
-    CR_SBASE = 3,           // [3..5] and_base & strict mask; [3] bits 15:0 zero
+    CR_SBASE = 3,           // [3..5] and_base & strict mask; [3] bits 15:0 (not part of the match test; leaves of at most
+                            // 16 classes): bit f set when the walk over the leaf may end after this class if class f
+                            // was the first strict match
     CR_INFO = 6,            // broad record index | has_broad << 12 | several members << 13 | relevant broad records << 16
     CR_ANY_FLAGS = 7,       // [15:0] OR of the members' choice flags; [31:16] the same in every class of a leaf:
                             // which of the leaf's first 16 classes have a broad record
@@ -112,8 +114,7 @@ enum : uint32_t {           // CR_INFO
     CI_LEAF_POS = 16,             // the upper halves hold one bit per class of the leaf (leaves of at most 16 classes):
                                   // CR_INFO: the classes with a broad record that still matters when this class is the
                                   // first strict match; CR_ANY_FLAGS of the leaf's first class: all classes with a broad
-                                  // record; CR_ANY_FLAGS of its second class: the classes whose strict match, as the first
-                                  // of the leaf, settles the outcome
+                                  // record
 };
 enum { BR_WORDS = 8 };      // broad record (hot): mask[3], base[3], pad
 // Per-flag table (cold) of a class with several members: for each of the 16 choice flags the
@@ -519,7 +520,7 @@ CB_HD bool class_strict(const FlatView& t, uint32_t ci, uint32_t c0h, uint32_t c
     const Quad a = HOT::q(t, t.at.classes[0] + ci * 4u);
     const Pair b = HOT::d(t, t.at.classes[1] + ci * 2u);
     *flags = a.x;
-    return (((c0h & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
+    return ((((c0h & a.x) ^ a.w) & 0xFFFF0000u) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
 }
 
 // Broad test of class `ci` given its info word (CR_INFO).
@@ -771,23 +772,21 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
         // Two cursors walk the leaf's run of classes; the bit that marks a class doubles as the loop counter
         // (1 <= count <= 16 here).
         typename HOT::Cursor p0 = HOT::at(t, t.at.classes[0] + start * 4u), p1 = HOT::at(t, t.at.classes[1] + start * 2u);
-        uint32_t bit = 1u;
+        uint32_t bit = 1u, may_end;
         const uint32_t end = 1u << count;
-        // Which classes settle the outcome when they are the first to match (a word of the whole leaf, kept with
-        // its second class; a leaf of one class reads its neighbour's, which cannot end its loop any earlier).
-        const uint32_t settles = HOT::w(t, t.at.class_info + start * 2u + 3u) >> CI_LEAF_POS;
 #pragma unroll 1
         do {
             const Quad a = HOT::q_at(p0);
             const Pair b = HOT::d_at(p1);
             p0 = HOT::step(p0, 4u); p1 = HOT::step(p1, 2u);
-            const bool hit = (((c0h & a.x) ^ a.w) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
+            const bool hit = ((((c0h & a.x) ^ a.w) & 0xFFFF0000u) | ((c1 & a.y) ^ b.x) | ((c2 & a.z) ^ b.y)) == 0;
             strict |= hit ? bit : 0u;
             any |= hit ? a.x : 0u;
             bit <<= 1;
-            // A first match that settles the outcome ends the lane's walk over the leaf: all of strict lies inside
-            // `settles` exactly when its only bit is such a class (a first match outside it stays in strict for good).
-        } while (bit != end && !((strict - 1u) < (strict & settles)));
+            // The low half of the first base word says after which first matches the walk may end here: nothing
+            // further down the leaf can change the outcome then.
+            may_end = strict & (0u - strict) & a.w;
+        } while (bit != end && !may_end);
     }
     uint32_t broad = 0;
     if ((leaf_ref & REF_BROAD) && (!strict || (leaf_ref & REF_BROAD_ALWAYS))) {

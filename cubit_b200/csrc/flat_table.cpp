@@ -423,26 +423,48 @@ struct TreeBuilder {
             }
             leaf_relevant |= relevant[k];
         }
-        // A class that, as the first strict match of the leaf, decides everything: no later class can outrank
-        // or tie it, no member of it or of a later class carries a flag that a rule could ask for under it, and
-        // no broad record matters next to it.  The kernel stops testing the leaf's classes there.
-        uint32_t settles = 0;
+        // How far the kernel has to test the leaf's classes once class f is the first strict match: up to the
+        // last class that can still change the outcome — a later class of f's group (it could outrank or tie f),
+        // a later class with a broad record that matters beside f (it has to be tested strictly before it is
+        // tested broadly), or a later class that carries a flag some rule could ask for: a flag that f, a later
+        // class that can match together with f, or one of f's own members carries and that some possible top
+        // candidate (f or a later class of its group) neither carries nor rules out.  Class i records, one bit
+        // per first match f <= i, whether the walk may end after it (bits 15:0 of its first base word, which the
+        // match test leaves out).
         if (order.size() <= 16) {
-            for (size_t ci = 0; ci < order.size(); ++ci) {
-                const uint32_t* rec = &ft.classes[(size_t(first_class) + ci) * CR_WORDS];
-                const bool no_later_rival = (rec[CR_GROUP] & 0xFFFFu & ~((2u << ci) - 1u)) == 0;
-                uint32_t later_flags = rec[CR_ANY_FLAGS] & 0xFFFFu;   // its own members count: a rule may ask for another of them
-                for (size_t cj = ci + 1; cj < order.size(); ++cj)
-                    if (can_both_match(order[ci], order[cj])) later_flags |= ft.classes[(size_t(first_class) + cj) * CR_WORDS + CR_ANY_FLAGS] & 0xFFFFu;
-                if (st[groups[order[ci]][0]].s_ok && relevant[ci] == 0 && no_later_rival && !(later_flags & ~rec[CR_FIRST_FLAGS]))
-                    settles |= 1u << ci;
+            std::vector<size_t> last(order.size());
+            for (size_t f = 0; f < order.size(); ++f) {
+                const uint32_t* rf = &ft.classes[(size_t(first_class) + f) * CR_WORDS];
+                last[f] = order.size() - 1;
+                if (!st[groups[order[f]][0]].s_ok) continue;   // never a strict match
+                const uint32_t later = ~((2u << f) - 1u) & 0xFFFFu;
+                const uint32_t rivals = rf[CR_GROUP] & later;
+                uint32_t common = rf[CR_FIRST_FLAGS] & 0xFFFFu, carried = rf[CR_ANY_FLAGS] & 0xFFFFu;
+                for (size_t c = f + 1; c < order.size(); ++c) {
+                    const uint32_t* rc = &ft.classes[(size_t(first_class) + c) * CR_WORDS];
+                    if ((rivals >> c) & 1u) common &= rc[CR_FIRST_FLAGS];
+                    if (can_both_match(order[f], order[c])) carried |= rc[CR_ANY_FLAGS] & 0xFFFFu;
+                }
+                const uint32_t asked = carried & ~common;
+                uint32_t needed = rivals | (relevant[f] & later);
+                for (size_t c = f + 1; c < order.size(); ++c)
+                    if (can_both_match(order[f], order[c]) && (ft.classes[(size_t(first_class) + c) * CR_WORDS + CR_ANY_FLAGS] & asked))
+                        needed |= 1u << c;
+                last[f] = f;
+                for (size_t c = f + 1; c < order.size(); ++c)
+                    if ((needed >> c) & 1u) last[f] = c;
+            }
+            for (size_t i = 0; i < order.size(); ++i) {
+                uint32_t done = 0;
+                for (size_t f = 0; f <= i; ++f)
+                    if (last[f] <= i) done |= 1u << f;
+                ft.classes[(size_t(first_class) + i) * CR_WORDS + CR_SBASE] |= done;
             }
         }
-        // Words of the whole leaf ride in the upper halves of the first two classes' flag words.
+        // Words of the whole leaf ride in the upper halves of the flag words.
         for (size_t ci = 0; ci < n16; ++ci)
             ft.classes[(size_t(first_class) + ci) * CR_WORDS + CR_INFO] |= relevant[ci] << CI_LEAF_POS;
         ft.classes[size_t(first_class) * CR_WORDS + CR_ANY_FLAGS] |= leaf_broad16 << CI_LEAF_POS;
-        if (order.size() > 1) ft.classes[(size_t(first_class) + 1) * CR_WORDS + CR_ANY_FLAGS] |= settles << CI_LEAF_POS;
         ft.n_leaves++;
         ft.max_leaf_classes = std::max<uint32_t>(ft.max_leaf_classes, uint32_t(order.size()));
         return REF_LEAF | first_class | (uint32_t(order.size()) << 20) | (leaf_has_broad ? uint32_t(REF_BROAD) : 0u) |
@@ -474,6 +496,14 @@ struct TreeBuilder {
     static constexpr uint32_t kFlattenBits = 6;
     uint32_t flatten_bits(uint32_t root) {
         if (!(root & REF_BIT)) return root;
+        // Fewer bits when no multiplier separates all assignments of the full set (one bit always works).
+        for (uint32_t max_bits = kFlattenBits; max_bits >= 1; --max_bits) {
+            const uint32_t r = flatten_bits(root, max_bits);
+            if (r) return r;
+        }
+        throw std::runtime_error("no perfect hash for a bit-node subtree");
+    }
+    uint32_t flatten_bits(uint32_t root, uint32_t max_bits) {
         std::vector<uint32_t> bits;
         {
             std::vector<uint32_t> queue{root};
@@ -482,7 +512,7 @@ struct TreeBuilder {
                 if (!(r & REF_BIT) || (r & REF_LEAF)) continue;
                 const uint32_t bit = (r >> 20) & 127u;
                 if (std::find(bits.begin(), bits.end(), bit) == bits.end()) {
-                    if (bits.size() >= kFlattenBits) continue;
+                    if (bits.size() >= max_bits) continue;
                     bits.push_back(bit);
                 }
                 queue.push_back(ft.children[ref_index(r)]);
@@ -531,7 +561,7 @@ struct TreeBuilder {
                 return write_node(node, mask, m, child_base, 32 - kk);
             }
         }
-        throw std::runtime_error("no perfect hash for a bit-node subtree");
+        return 0;
     }
     // Replaces every bit node reachable from `dir` (entries added on the way are visited too).
     void flatten_all(std::vector<uint32_t>& dir) {
