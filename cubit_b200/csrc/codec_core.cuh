@@ -233,7 +233,10 @@ struct BlobLayout {
     uint32_t enc_stride;
     uint32_t var[2];      // variant records (encode side, two quad planes) directly follow the deposit records
     uint32_t enc_end;     // encode window: [enc, enc_end) holds the deposit and variant records
-    uint32_t flagbest, gfields, metaf;
+    uint32_t flagbest;    // per class with several members: FB_WORDS, for each choice flag {key, variant | extraction record << 16} of the best member carrying it
+    uint32_t leafbest;    // per leaf (at the index of its first class): FB_WORDS, for each choice flag that exactly one class of the leaf
+                          // carries {1 | tie << 1, variant | extraction record << 16} of that class's best member carrying it, else {0, 0}
+    uint32_t gfields, metaf;
     uint32_t gindex;      // per variant: first generator field | field count << 24 (into gfields)
     uint32_t rt[2];       // roundtrip constants: per variant {A0, A1, A2, E3 | mask index << 9}; per distinct mask
                           // {~M0, ~M1, ~M2, reuse keep | const << 3}.  The two planes are adjacent and end the blob
@@ -846,13 +849,23 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     if (need && !(first_fl & need)) {
         // Second pass (uncommon): best member carrying `need` among the matching classes.
         uint32_t win_key = 0xFFFFFFFFu, win_best = FORM_NONE, tie2 = 0;
-        // Which matching classes have a member that carries it (the flags ride in the first mask word).
+        // When one class of the whole leaf carries the flag, that class is among the matches (the flag came from
+        // there) and the table compiler has the answer.
+        const uint32_t* known = t.cold + t.at.leafbest + start * FB_WORDS + 2u * cb_lowest_bit(need);
+        const uint32_t how = cb_ld(known);
+        // Otherwise: which matching classes have a member that carries it (the flags ride in the first mask word).
         uint32_t cand = 0;
-        for (uint32_t left = strict | broad; left; left &= left - 1u) {
-            const uint32_t i = cb_lowest_bit(left);
-            cand |= (HOT::w(t, t.at.classes[0] + (start + i) * 4u) & need) ? (1u << i) : 0u;
+        if (!(how & 1u)) {
+            for (uint32_t left = strict | broad; left; left &= left - 1u) {
+                const uint32_t i = cb_lowest_bit(left);
+                cand |= (HOT::w(t, t.at.classes[0] + (start + i) * 4u) & need) ? (1u << i) : 0u;
+            }
         }
-        if (cand && !(cand & (cand - 1u))) {
+        if (how & 1u) {
+            win_best = cb_ld(known + 1);
+            tie2 = (how >> 1) & 1u;
+            win_key = 0;
+        } else if (cand && !(cand & (cand - 1u))) {
             // One such class (five times in six): its best member with the flag wins, there are no keys to compare.
             const uint32_t ci = start + cb_lowest_bit(cand);
             if (HOT::w(t, t.at.class_info + ci * 2u) & CI_SEVERAL) {

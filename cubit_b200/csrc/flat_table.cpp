@@ -461,6 +461,27 @@ struct TreeBuilder {
                 ft.classes[(size_t(first_class) + i) * CR_WORDS + CR_SBASE] |= done;
             }
         }
+        // The second pass asks for the best member that carries one flag among the matching classes.  When exactly
+        // one class of the leaf carries the flag at all, the answer does not depend on the word.
+        if (order.size() <= 16) {
+            ft.leafbest.resize((size_t(first_class) + 1) * FB_WORDS, 0);
+            uint32_t* lb = &ft.leafbest[size_t(first_class) * FB_WORDS];
+            for (uint32_t f = 0; f < 16; ++f) {
+                size_t carrier = order.size(), carriers = 0;
+                for (size_t c = 0; c < order.size(); ++c)
+                    if ((ft.classes[(size_t(first_class) + c) * CR_WORDS + CR_ANY_FLAGS] >> f) & 1u) { carrier = c; ++carriers; }
+                if (carriers != 1) continue;
+                const uint32_t* rc = &ft.classes[(size_t(first_class) + carrier) * CR_WORDS];
+                if (rc[CR_INFO] & CI_SEVERAL) {
+                    const uint32_t* fb = &ft.flagbest[size_t(rc[CR_FLAGBEST]) * FB_WORDS];
+                    lb[2 * f] = 1u | ((fb[2 * f] & KEY_WITHIN) ? 2u : 0u);
+                    lb[2 * f + 1] = fb[2 * f + 1];
+                } else {
+                    lb[2 * f] = 1u;
+                    lb[2 * f + 1] = rc[CR_BEST];
+                }
+            }
+        }
         // Words of the whole leaf ride in the upper halves of the flag words.
         for (size_t ci = 0; ci < n16; ++ci)
             ft.classes[(size_t(first_class) + ci) * CR_WORDS + CR_INFO] |= relevant[ci] << CI_LEAF_POS;
@@ -1146,6 +1167,8 @@ FlatTable FlatTable::compile(const IsaTable& t) {
     while (ft.blob.size() % 4) ft.blob.push_back(0);
     L.enc_end = uint32_t(ft.blob.size());
     L.flagbest = place(ft.flagbest);
+    ft.leafbest.resize(std::max<size_t>(ft.leafbest.size(), (ft.classes.size() / CR_WORDS) * FB_WORDS), 0);
+    L.leafbest = place(ft.leafbest);
     L.gfields = place(ft.gfields);
     L.metaf = place(ft.metaf);
     L.gindex = place(ft.gindex);

@@ -37,6 +37,7 @@ struct FlatTable {
     std::vector<uint32_t> children;  // refs
     std::vector<uint32_t> classes;   // CR_WORDS each
     std::vector<uint32_t> flagbest;  // FB_WORDS per class, indexed by the class; filled for classes that have several members
+    std::vector<uint32_t> leafbest;  // FB_WORDS per class index, filled at the first class of every leaf of at most 16 classes
     std::vector<uint32_t> broad;     // BR_WORDS each
     std::vector<uint32_t> ext;       // XR_WORDS per distinct field layout
     std::vector<uint32_t> enc;       // ER_WORDS per distinct field layout: the encoder's view of `ext`

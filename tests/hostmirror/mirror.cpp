@@ -61,11 +61,11 @@ void mir_info(void* h, uint32_t* out) {
                             f.max_leaf_classes, f.max_depth, f.at.hot_words * 4, f.at.total_words * 4};
     for (int i = 0; i < 12; ++i) out[i] = v[i];
 }
-// The compiled table blob and its section offsets (BlobLayout as 30 u32).
+// The compiled table blob and its section offsets (BlobLayout as 31 u32).
 void mir_blob(void* h, const uint32_t** blob, uint32_t* layout_words) {
     Mirror* m = (Mirror*)h;
     *blob = m->flat.blob.data();
-    static_assert(sizeof(BlobLayout) == 30 * sizeof(uint32_t), "layout size");
+    static_assert(sizeof(BlobLayout) == 31 * sizeof(uint32_t), "layout size");
     memcpy(layout_words, &m->flat.at, sizeof(BlobLayout));
 }
 // Per word: classes in its leaf, classes that match, tree steps walked (for tuning).
