@@ -61,6 +61,12 @@ def mirror():
             lib.mir_synth_batch(h, mix, C.c_uint64(seed), noise, C.c_uint64(first), C.c_uint64(n), C.c_void_p(words.ctypes.data),
                                 C.c_void_p(form.ctypes.data), C.c_void_p(slots.ctypes.data), C.c_void_p(ctrl.ctypes.data), T)
             return words, form, slots, ctrl
+        def blob(self):
+            ptr = C.POINTER(C.c_uint32)()
+            layout = np.zeros(31, np.uint32)
+            lib.mir_blob(h, C.byref(ptr), C.c_void_p(layout.ctypes.data))
+            return np.ctypeslib.as_array(ptr, shape=(int(layout[29]),)).copy(), layout
+
         def word_meta(self, words):
             n = len(words)
             mr = np.zeros(n, np.uint32); bm = np.zeros(n, np.uint32); ex = np.zeros(n, np.uint8)
@@ -156,3 +162,34 @@ def test_fused_roundtrip_equals_decode_encode_compare(mirror, oracle):
     assert (fused == unfused).all()
     assert (fused == oracle.roundtrip_batch(words, threads=T)).all()
     assert np.bincount(fused, minlength=3).min() > 1000
+
+
+def test_static_words_of_the_table_compiler_are_consistent(mirror):
+    """What the table compiler settles ahead of the kernel, checked on the compiled blob itself, leaf by leaf (leaves of at
+    most 16 classes): "the walk may end after this class if class f was the first strict match" only ever switches on
+    further down a leaf and never speaks of a class below the one that records it; and a second-pass answer is recorded for a flag exactly when one class of the leaf carries it."""
+    blob, at = mirror.blob()
+    dir_, children, cls0, cls2, info, leafbest = (int(at[k]) for k in (0, 3, 4, 6, 8, 23))
+    refs = np.concatenate([blob[dir_:dir_ + 4096], blob[children:cls0]])
+    leaves = np.unique(refs[(refs >> 31) == 1])
+    assert len(leaves) > 1000
+    checked = answers = 0
+    for ref in leaves.tolist():
+        start, count = ref & 0xFFFFF, (ref >> 20) & 0xFF
+        if count > 16:
+            continue
+        done = [int(blob[cls0 + (start + i) * 4 + 3]) & 0xFFFF for i in range(count)]
+        flags = [int(blob[cls0 + (start + i) * 4]) & 0xFFFF for i in range(count)]
+        if done == [0] * count and flags == [0] * count and int(blob[cls0 + start * 4 + 3]) == 0x10000:
+            continue                                                  # the class that never matches (an empty leaf)
+        for i in range(count):
+            assert done[i] >> (i + 1) == 0, (ref, i)                  # only first matches at or above this class
+            if i:
+                assert done[i - 1] & ~done[i] == 0, (ref, i)          # once the walk may end it may end later too
+        for f in range(16):
+            carriers = sum((fl >> f) & 1 for fl in flags)
+            known = int(blob[leafbest + start * 32 + 2 * f]) & 1
+            assert known == (1 if carriers == 1 else 0), (ref, f)
+            answers += known
+        checked += 1
+    assert checked > 1000 and answers > 500
