@@ -502,8 +502,8 @@ CB_HD uint32_t find_leaf(const FlatView& t, uint32_t c0, uint32_t c1, uint32_t c
     if (ref == 0) return ST_NO_OPCODE;
     // The table compiler folds every chain of bit nodes into a hash node over their bits, so
     // the walk meets hash nodes only.
-    // Nine words in ten take at least one step, two in ten a second one: both stand outside the loop.
-    if (!(ref & REF_LEAF)) ref = node_step<HOT>(t, ref, c0, c1, c2);
+    // Nine words in ten take one step, hardly any a second one (the table compiler folds small levels into one
+    // node): the first stands outside the loop.
     if (!(ref & REF_LEAF)) ref = node_step<HOT>(t, ref, c0, c1, c2);
     while (!(ref & REF_LEAF)) ref = node_step<HOT>(t, ref, c0, c1, c2);
     *start = ref_index(ref);
