@@ -137,9 +137,9 @@ STREAM_SEED = 1
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per word of one captured launch, from the newest ncu summaries
 # under profiles/ (8 Mi-word captures, scaled by the word count: the traffic is the stream itself, read
-# and written once).  decode: (134.45 MB + 261.35 MB) / 8 Mi words; encode: (319.2 MB + 98.1 MB) / 8 Mi;
-# roundtrip: (134.46 MB + 5.77 MB) / 8 Mi.  Part of the last writes of a captured launch is still in L2 when it ends.
-NCU_DRAM_BYTES_PER_WORD = {"decode": 47.18, "encode": 49.74, "roundtrip": 16.72}
+# and written once).  decode: (134.46 MB + 261.45 MB) / 8 Mi words; encode: (319.2 MB + 98.1 MB) / 8 Mi;
+# roundtrip: (134.47 MB + 6.85 MB) / 8 Mi.  Part of the last writes of a captured launch is still in L2 when it ends.
+NCU_DRAM_BYTES_PER_WORD = {"decode": 47.20, "encode": 49.74, "roundtrip": 16.85}
 # The capture each figure comes from (summaries under profiles/).
 NCU_CAPTURE = {"decode": "profiles/decode_kernel_zipf.md", "encode": "profiles/encode_kernel_records.md",
                "roundtrip": "profiles/roundtrip_kernel_mix.md"}

@@ -4,7 +4,7 @@
 // consecutive 16-byte words (512 contiguous bytes) and writes 32 consecutive entries of
 // every output plane, so all global traffic is coalesced and uses streaming hints.  The
 // per-word table lookups are data dependent and diverge between lanes, so the hot part of
-// the ISA table (about 200 KB) is staged into shared memory once per CTA by persistent
+// the ISA table (about 215 KB) is staged into shared memory once per CTA by persistent
 // CTAs (one per SM, 1024 threads); small batches use a variant that reads the table through
 // the read-only global path instead of paying for the staging.
 #include <cuda_runtime.h>

@@ -53,7 +53,7 @@ namespace cubit {
 // for a member other than the best one.
 //
 // All tables live in one blob of u32.  Its first part ("hot": everything a decode touches
-// per word, under 200 KB for the SM120 table) is copied into shared memory by the kernels;
+// per word, 215 KB for the SM120 table) is copied into shared memory by the kernels;
 // the rest ("cold": rarely needed data and the encode / generator tables) stays in global
 // memory.  Records are 16-byte aligned and read with 128-bit loads.
 
