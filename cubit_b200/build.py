@@ -4,6 +4,7 @@ Usage: ``python -m cubit_b200.build [--force] [--verbose]``.  nvcc cross-compile
 """
 from __future__ import annotations
 
+import fcntl
 import os
 import shutil
 import subprocess
@@ -36,20 +37,34 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles the library if it is missing or older than its sources; returns its path."""
+    """Compiles the library if it is missing or older than its sources; returns its path.
+
+    Several processes may call this at once (one rank per GPU under torchrun): one of them compiles, into a file of
+    its own that takes the library's name only when it is complete, and the others wait for it."""
     if not force and not is_stale():
         return LIB
     LIB_DIR.mkdir(exist_ok=True)
-    cmd = [nvcc_path(), "-O3", "-std=c++17", "-lineinfo", *ARCH, "-shared", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function,-Wno-unknown-pragmas",
-           "-cudart", "static", "-o", str(LIB)] + [str(CSRC / s) for s in SOURCES] + ["-ldl", "-lpthread"]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-        print(" ".join(cmd), file=sys.stderr)
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-    if verbose:
-        print(proc.stdout + proc.stderr, file=sys.stderr)
+    with open(LIB_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():      # another process built it while this one waited
+                return LIB
+            tmp = LIB_DIR / f".libcubit_b200.{os.getpid()}.so"
+            cmd = [nvcc_path(), "-O3", "-std=c++17", "-lineinfo", *ARCH, "-shared", "-Xcompiler",
+                   "-fPIC,-Wall,-Wno-unused-function,-Wno-unknown-pragmas", "-cudart", "static", "-o", str(tmp)] \
+                  + [str(CSRC / s) for s in SOURCES] + ["-ldl", "-lpthread"]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+                print(" ".join(cmd), file=sys.stderr)
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+            if verbose:
+                print(proc.stdout + proc.stderr, file=sys.stderr)
+            os.replace(tmp, LIB)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 
