@@ -762,13 +762,15 @@ CB_HD uint32_t select_variant(const FlatView& t, uint32_t c0, uint32_t c1, uint3
     }
 
     // Every leaf has at least one class (an empty one holds the class that never matches), so the
-    // first test runs for all lanes of a warp together.  Strict tests for every class first,
-    // collecting the union of choice flags over the matching candidates (they ride in the unused
-    // low half of the first mask word); the classes that failed but have a broad record are tested
-    // in a loop of their own, and only in leaves whose ref says that there are any (one word in
-    // three has one; inside the first loop the branch would be taken by some lane of the warp in
-    // nearly every iteration).  Which classes of the leaf have a broad record, and which of those
-    // still matter once some class matched strictly, are constants of the leaf kept with every class.
+    // first test runs for all lanes of a warp together.  Strict tests first, class by class in rank
+    // order, collecting the union of choice flags over the matching candidates (they ride in the
+    // unused low half of the first mask word), until the table says that nothing further down the
+    // leaf can change the outcome (most words stop at their first match: 1.3 tests per word);
+    // the classes that failed but have a broad record are tested in a loop of their own, and only
+    // in leaves whose ref says that there are any (inside the first loop the branch would be taken
+    // by some lane of the warp in nearly every iteration).  Which classes of the leaf have a broad
+    // record, and which of those still matter beside a given first strict match, are constants
+    // kept with the classes.
     const uint32_t c0h = class_limb0(c0);
     uint32_t strict = 0, any = 0;
     {
